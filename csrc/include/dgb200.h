@@ -1,0 +1,203 @@
+// Public C ABI of the dummygrad_b200 kernel library (libdgb200.so).
+//
+// Every launcher takes raw device pointers and a CUDA stream, allocates nothing
+// unless stated, and returns 0 on success or a negative DG_ERR_* / positive
+// cudaError_t code. The Python front end binds these through ctypes; the C++
+// shim headers call them directly.
+#pragma once
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { DG_F32 = 0, DG_BF16 = 1 } dg_dtype;
+
+enum {
+  DG_OK = 0,
+  DG_ERR_BAD_ARG = -1,
+  DG_ERR_UNSUPPORTED = -2,
+  DG_ERR_DRIVER = -3,
+  DG_ERR_TOO_LARGE = -4,
+};
+
+// Broadcast mode of a secondary operand relative to the primary [batch, r, c] tensor.
+enum {
+  DG_BC_SAME = 0,    // same shape as the output
+  DG_BC_ROW = 1,     // [1, c]   : index = i % c
+  DG_BC_COL = 2,     // [r, 1]   : index = (i / c) % r
+  DG_BC_SCALAR = 3,  // [1, 1]
+  DG_BC_MAT = 4,     // [r, c]   : index = i % (r*c)  (broadcast over batch)
+  DG_BC_ROWS = 5,    // [batch*r, 1] keepdim-last reduction result: index = i / c
+  DG_BC_COLS = 6,    // [batch, 1, c] keepdim-rows reduction result: index = (i/(r*c))*c + i%c
+};
+
+// Elementwise opcodes (K8 family). x is the primary operand; y, z, w are optional.
+enum {
+  DG_EW_COPY = 0,      // x (with dtype cast when in/out dtypes differ)
+  DG_EW_ADD, DG_EW_SUB, DG_EW_MUL, DG_EW_DIV,          // x ∘ y
+  DG_EW_ADD_S, DG_EW_MUL_S, DG_EW_DIV_S, DG_EW_RSUB_S, DG_EW_RDIV_S,  // x ∘ s0
+  DG_EW_POW_I,         // x^(int)s0
+  DG_EW_SQRT, DG_EW_LOG_EPS /* log(x+s0) */, DG_EW_EXP,
+  DG_EW_RELU, DG_EW_TANH, DG_EW_GELU,
+  DG_EW_NEG,
+  DG_EW_COPY_Y,        // y broadcast to output shape
+  DG_EW_MASK_FILL,     // y==0 ? s0 : x
+  DG_EW_CAUSAL_FILL,   // col>row ? s0 : x
+  DG_EW_CLAMP,         // min(max(x,s0),s1)
+  DG_EW_FMA_S,         // x*s0 + y*s1
+  // backward formulas: x = incoming gradient g
+  DG_EW_DIV_BWD_B,     // -x*z/(y*y)            (y=b, z=a)
+  DG_EW_POW_BWD,       // s0*y^(s0-1)*x         (y=a)
+  DG_EW_SQRT_BWD,      // 0.5*x/sqrt(y)         (y=a)
+  DG_EW_LOG_BWD,       // x/(y+s0)
+  DG_EW_RDIV_BWD,      // -s0*x/(y*y)
+  DG_EW_RELU_BWD,      // y>0 ? x : 0
+  DG_EW_TANH_BWD,      // (1-y*y)*x             (y=out)
+  DG_EW_GELU_BWD,      // gelu'(y)*x
+  DG_EW_MASK_BWD,      // y!=0 ? x : 0
+  DG_EW_CAUSAL_BWD,    // col<=row ? x : 0
+  DG_EW_VAR_BWD,       // s0*(x - y)*z          (x=a, y=mean, z=g)
+  DG_EW_STD_BWD,       // s0*(x - y)*z/(w+s1)   (x=a, y=mean, z=g, w=std)
+  DG_EW_XENT_PROB_BWD, // -(y/x)*s0*z          (x=p, y=t, z=g)
+  DG_EW_MSE_BWD,       // s0*(x - y)*z          (x=pred, y=target, z=g)
+  DG_EW_SCALE_SHIFT,   // x*y + z               (y=gamma, z=beta, usually DG_BC_ROW)
+  DG_EW_NUM_OPS
+};
+
+// out[i] = op(x[i], y[bc], z[bc], w[bc]); n = batch*r*c elements.
+int dg_elementwise(int op, int dtype, void* out, const void* x, const void* y, const void* z,
+                   const void* w, int ymode, int zmode, int wmode, float s0, float s1,
+                   int64_t n, int64_t r, int64_t c, cudaStream_t stream);
+// dtype-converting copy: out_dtype[out] = in_dtype[in].
+int dg_cast(int out_dtype, void* out, int in_dtype, const void* in, int64_t n, cudaStream_t stream);
+// in-place accumulate: dst += src  (dtype of both).
+int dg_accumulate(int dtype, void* dst, const void* src, int64_t n, cudaStream_t stream);
+
+// K10: strided copy. dst and src described by ndim (<=8) shape with element strides.
+int dg_strided_copy(int dtype, void* dst, const int64_t* dst_strides, const void* src,
+                    const int64_t* src_strides, const int64_t* shape, int ndim, cudaStream_t stream);
+// batched 2-D transpose: in [B, R, C] contiguous -> out [B, C, R] contiguous.
+int dg_transpose2d(int dtype, void* out, const void* in, int64_t B, int64_t R, int64_t C,
+                   cudaStream_t stream);
+
+// K9 reductions. mode: 0 sum, 1 mean, 2 biased variance, 3 sqrt(biased variance).
+enum { DG_RED_SUM = 0, DG_RED_MEAN = 1, DG_RED_VAR = 2, DG_RED_STD = 3 };
+// rows: x[R, C] -> out[R] ; optional mean_out[R] (may be null) for VAR/STD.
+int dg_reduce_rows(int dtype, void* out, void* mean_out, const void* x, int64_t R, int64_t C,
+                   int mode, cudaStream_t stream);
+// cols: x[B, R, C] -> out[B, C]; scratch must hold dg_reduce_cols_scratch_bytes() bytes.
+int64_t dg_reduce_cols_scratch_bytes(int64_t B, int64_t R, int64_t C);
+int dg_reduce_cols(int dtype, void* out, void* mean_out, const void* x, int64_t B, int64_t R,
+                   int64_t C, int mode, void* scratch, cudaStream_t stream);
+// full sum -> out[1] (dtype of x, fp32 accumulate, fixed order); scratch >= 1024 floats.
+int dg_sum_all(int dtype, void* out, const void* x, int64_t n, float scale, void* scratch,
+               cudaStream_t stream);
+
+// K5 softmax with optional scale and mask. mask_mode: 0 none, 1 causal (col>row), 2 tensor (==0 masked).
+int dg_softmax_fwd(int dtype, void* out, const void* x, const void* mask, int mask_mode, float scale,
+                   int64_t rows, int64_t r, int64_t c, cudaStream_t stream);
+int dg_softmax_bwd(int dtype, void* gx, const void* g, const void* out, const void* mask,
+                   int mask_mode, float scale, int64_t rows, int64_t r, int64_t c,
+                   cudaStream_t stream);
+
+// K4 LayerNorm over the last dim (biased variance, eps inside the sqrt).
+int dg_layernorm_fwd(int dtype, void* y, float* mean, float* rstd, const void* x, const void* gamma,
+                     const void* beta, int64_t rows, int64_t d, float eps, cudaStream_t stream);
+int64_t dg_layernorm_bwd_scratch_bytes(int64_t rows, int64_t d);
+int dg_layernorm_bwd(int dtype, void* dx, void* dgamma, void* dbeta, const void* g, const void* x,
+                     const void* gamma, const float* mean, const float* rstd, int64_t rows,
+                     int64_t d, void* scratch, cudaStream_t stream);
+
+// K6 embedding gather (+ optional positional table add) and scatter-add.
+int dg_embedding_fwd(int dtype, void* out, const void* table, const int64_t* idx, const void* pos_table,
+                     const int64_t* pos_idx, int64_t n, int64_t d, int64_t vocab, cudaStream_t stream);
+// dtable[idx[t], :] += g[t, :]; dtable is fp32 or bf16 per dtype; must be pre-initialised.
+int dg_embedding_bwd(int dtype, void* dtable, const void* g, const int64_t* idx, int64_t n, int64_t d,
+                     int64_t vocab, cudaStream_t stream);
+// float-encoded indices (reference convention) -> int64, bounds flag written to *bad (device int).
+int dg_index_from_float(int64_t* out, const float* in, int64_t n, int64_t limit, int* bad,
+                        cudaStream_t stream);
+int dg_one_hot(float* out, const int64_t* idx, int64_t n, int64_t classes, cudaStream_t stream);
+
+// K7 fused softmax-cross-entropy on logits. loss_rows[T] fp32 = lse - logit[target];
+// dlogits (may alias logits) = (softmax - onehot) * grad_scale.
+int dg_xent_fwd_bwd(int dtype, float* loss_rows, float* lse, void* dlogits, const void* logits,
+                    const int64_t* target, int64_t T, int64_t V, int64_t ld, float grad_scale,
+                    cudaStream_t stream);
+
+// K11 optimizers. master may be null (then p is the fp32 master itself).
+// Adam/AdamW: bias correction by step t; weight_decay decoupled (AdamW) when wd != 0.
+int dg_adam_step(int p_dtype, void* p, float* master, int g_dtype, const void* g, float* m, float* v,
+                 int64_t n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                 float grad_scale, cudaStream_t stream);
+int dg_sgd_step(int p_dtype, void* p, float* master, int g_dtype, const void* g, int64_t n, float lr,
+                float grad_scale, cudaStream_t stream);
+// multi-tensor Adam over a device-resident table (see optim.cu for the record layout).
+typedef struct {
+  void* p; float* master; const void* g; float* m; float* v; int64_t n; int32_t step; int32_t pad;
+} dg_adam_rec;
+int dg_adam_multi(int p_dtype, int g_dtype, const dg_adam_rec* recs_dev, const int64_t* chunk_dev,
+                  int64_t n_chunks, int64_t chunk_elems, float lr, float beta1, float beta2, float eps,
+                  float wd, float grad_scale, cudaStream_t stream);
+
+// K12 Philox normal fill: out = mean + std * N(0,1).
+int dg_randn(int dtype, void* out, int64_t n, uint64_t seed, uint64_t offset, float mean, float std,
+             cudaStream_t stream);
+int dg_fill(int dtype, void* out, int64_t n, float value, cudaStream_t stream);
+
+// SIMT batched GEMM with arbitrary element strides (fp32 accumulate). C[b] = alpha*A[b]*B[b] + beta*C[b].
+// a_bs/b_bs/c_bs: batch strides (0 broadcasts); (ars,acs) row/col strides of A[M,K], etc.
+int dg_gemm_simt(int dtype, void* C, const void* A, const void* B, int64_t batch, int64_t M, int64_t N,
+                 int64_t K, int64_t a_bs, int64_t ars, int64_t acs, int64_t b_bs, int64_t brs,
+                 int64_t bcs, int64_t c_bs, int64_t crs, float alpha, float beta, cudaStream_t stream);
+
+// K1/K2 tcgen05 bf16 GEMM. D[M,N] = epilogue(A[M,K] * B[K,N]).
+//  a_kmajor: 1 -> A stored [M,K] row-major (lda = row stride); 0 -> stored [K,M] row-major (A^T).
+//  b_kmajor: 1 -> B stored [N,K] row-major (ldb);               0 -> stored [K,N] row-major.
+//  out_dtype DG_BF16 or DG_F32. bias[N] (bf16/fp32 per bias_dtype) optional.
+//  epi: see DG_EPI_*. aux: pre-activation output (GELU) or input (DGELU), bf16 [M,N] ld=ldd.
+//  residual: optional bf16/fp32 (out dtype) [M,N] ld=ldd added after activation (may alias D).
+enum { DG_EPI_NONE = 0, DG_EPI_GELU = 1, DG_EPI_DGELU = 2, DG_EPI_RELU = 3, DG_EPI_DRELU = 4 };
+typedef struct {
+  const void* A; const void* B; void* D;
+  const void* bias; void* aux; const void* residual;
+  int64_t M, N, K, batch;
+  int64_t lda, ldb, ldd;
+  int64_t a_bs, b_bs, d_bs;   // batch strides in elements (0: operand shared by all batch entries)
+  int64_t bias_bs;            // bias stride between batch entries (0: shared)
+  int a_kmajor, b_kmajor, out_dtype, bias_dtype, epi;
+  float alpha;
+  int* status;                // optional device int: set non-zero when a bounded wait expires
+} dg_gemm_args;
+int dg_gemm_sm100(const dg_gemm_args* args, cudaStream_t stream);
+int dg_gemm_sm100_supported(const dg_gemm_args* args);  // 1 if alignment/shape rules are met
+
+// K3 fused causal attention (bf16, head_dim 64 or 128). q,k,v,o: [B, S, H, dk] with row strides.
+typedef struct {
+  const void* q; const void* k; const void* v; void* o; float* lse;   // lse [B,H,S]
+  int64_t B, H, S, dk;
+  int64_t q_row, k_row, v_row, o_row;      // element stride between successive tokens
+  int64_t q_bs, k_bs, v_bs, o_bs;          // batch strides
+  float scale; int causal; int* status;
+} dg_attn_fwd_args;
+int dg_attention_fwd_sm100(const dg_attn_fwd_args* a, cudaStream_t stream);
+typedef struct {
+  const void* q; const void* k; const void* v; const void* o; const void* d_o; const float* lse;
+  void* dq; void* dk_; void* dv; float* delta;   // delta [B,H,S] scratch; dq_acc fp32 scratch
+  float* dq_acc;
+  int64_t B, H, S, dk;
+  int64_t row;      // common token stride of q,k,v,o,do,dq,dk,dv (elements)
+  int64_t bs;       // common batch stride
+  float scale; int causal; int* status;
+} dg_attn_bwd_args;
+int dg_attention_bwd_sm100(const dg_attn_bwd_args* a, cudaStream_t stream);
+
+// Library/device info.
+int dg_version(void);
+int dg_device_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,257 @@
+// K8: elementwise / broadcast / activation family, forward and backward formulas.
+//
+// One templated kernel covers every pointwise op of the reference (src/ops.h,
+// src/scalar_ops.h, src/broadcasting.h, src/activations.h, src/masking.h): the
+// opcode is a template parameter, secondary operands carry a broadcast mode, and a
+// 16-byte-per-thread vector path is taken when every operand has the output's shape.
+#include "common.cuh"
+
+namespace dg {
+
+struct EwParams {
+  float s0, s1;
+  int64_t n, r, c;
+  int ymode, zmode, wmode;
+};
+
+__device__ __forceinline__ int64_t bc_index(int mode, int64_t i, int64_t r, int64_t c) {
+  switch (mode) {
+    case DG_BC_SAME: return i;
+    case DG_BC_ROW: return i % c;
+    case DG_BC_COL: return (i / c) % r;
+    case DG_BC_SCALAR: return 0;
+    case DG_BC_MAT: return i % (r * c);
+    case DG_BC_ROWS: return i / c;
+    case DG_BC_COLS: return (i / (r * c)) * c + i % c;
+  }
+  return i;
+}
+
+template <int OP> struct OpTraits {
+  static constexpr bool uses_x = (OP != DG_EW_COPY_Y);
+  static constexpr bool uses_y =
+      (OP == DG_EW_ADD || OP == DG_EW_SUB || OP == DG_EW_MUL || OP == DG_EW_DIV || OP == DG_EW_COPY_Y ||
+       OP == DG_EW_MASK_FILL || OP == DG_EW_FMA_S || OP >= DG_EW_DIV_BWD_B) &&
+      OP != DG_EW_CAUSAL_BWD;
+  static constexpr bool uses_z = (OP == DG_EW_DIV_BWD_B || OP == DG_EW_VAR_BWD || OP == DG_EW_STD_BWD ||
+                                  OP == DG_EW_XENT_PROB_BWD || OP == DG_EW_MSE_BWD || OP == DG_EW_SCALE_SHIFT);
+  static constexpr bool uses_w = (OP == DG_EW_STD_BWD);
+  static constexpr bool uses_index = (OP == DG_EW_CAUSAL_FILL || OP == DG_EW_CAUSAL_BWD);
+};
+
+template <int OP>
+__device__ __forceinline__ float ew_apply(float x, float y, float z, float w, float s0, float s1,
+                                          int64_t row, int64_t col) {
+  if constexpr (OP == DG_EW_COPY) return x;
+  else if constexpr (OP == DG_EW_ADD) return x + y;
+  else if constexpr (OP == DG_EW_SUB) return x - y;
+  else if constexpr (OP == DG_EW_MUL) return x * y;
+  else if constexpr (OP == DG_EW_DIV) return x / y;
+  else if constexpr (OP == DG_EW_ADD_S) return x + s0;
+  else if constexpr (OP == DG_EW_MUL_S) return x * s0;
+  else if constexpr (OP == DG_EW_DIV_S) return x / s0;
+  else if constexpr (OP == DG_EW_RSUB_S) return s0 - x;
+  else if constexpr (OP == DG_EW_RDIV_S) return s0 / x;
+  else if constexpr (OP == DG_EW_POW_I) {
+    int n = (int)s0;
+    bool neg = n < 0;
+    unsigned e = neg ? (unsigned)(-n) : (unsigned)n;
+    float b = x, acc = 1.f;
+    while (e) { if (e & 1u) acc *= b; b *= b; e >>= 1; }
+    return neg ? 1.f / acc : acc;
+  }
+  else if constexpr (OP == DG_EW_SQRT) return sqrtf(x);
+  else if constexpr (OP == DG_EW_LOG_EPS) return logf(x + s0);
+  else if constexpr (OP == DG_EW_EXP) return expf(x);
+  else if constexpr (OP == DG_EW_RELU) return x > 0.f ? x : 0.f;
+  else if constexpr (OP == DG_EW_TANH) return tanhf(x);
+  else if constexpr (OP == DG_EW_GELU) return gelu_f(x);
+  else if constexpr (OP == DG_EW_NEG) return -x;
+  else if constexpr (OP == DG_EW_COPY_Y) return y;
+  else if constexpr (OP == DG_EW_MASK_FILL) return y == 0.f ? s0 : x;
+  else if constexpr (OP == DG_EW_CAUSAL_FILL) return col > row ? s0 : x;
+  else if constexpr (OP == DG_EW_CLAMP) return fminf(fmaxf(x, s0), s1);
+  else if constexpr (OP == DG_EW_FMA_S) return x * s0 + y * s1;
+  else if constexpr (OP == DG_EW_DIV_BWD_B) return -x * z / (y * y);
+  else if constexpr (OP == DG_EW_POW_BWD) {
+    int n = (int)s0 - 1;
+    bool neg = n < 0;
+    unsigned e = neg ? (unsigned)(-n) : (unsigned)n;
+    float b = y, acc = 1.f;
+    while (e) { if (e & 1u) acc *= b; b *= b; e >>= 1; }
+    acc = neg ? 1.f / acc : acc;
+    return s0 * acc * x;
+  }
+  else if constexpr (OP == DG_EW_SQRT_BWD) return 0.5f * x / sqrtf(y);
+  else if constexpr (OP == DG_EW_LOG_BWD) return x / (y + s0);
+  else if constexpr (OP == DG_EW_RDIV_BWD) return -s0 * x / (y * y);
+  else if constexpr (OP == DG_EW_RELU_BWD) return y > 0.f ? x : 0.f;
+  else if constexpr (OP == DG_EW_TANH_BWD) return (1.f - y * y) * x;
+  else if constexpr (OP == DG_EW_GELU_BWD) return gelu_grad_f(y) * x;
+  else if constexpr (OP == DG_EW_MASK_BWD) return y != 0.f ? x : 0.f;
+  else if constexpr (OP == DG_EW_CAUSAL_BWD) return col <= row ? x : 0.f;
+  else if constexpr (OP == DG_EW_VAR_BWD || OP == DG_EW_MSE_BWD) return s0 * (x - y) * z;
+  else if constexpr (OP == DG_EW_STD_BWD) return s0 * (x - y) * z / (w + s1);
+  else if constexpr (OP == DG_EW_XENT_PROB_BWD) return -(y / x) * s0 * z;
+  else if constexpr (OP == DG_EW_SCALE_SHIFT) return x * y + z;
+  else return x;
+}
+
+// Scalar (any broadcast) path.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) ew_scalar_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                        const T* __restrict__ y, const T* __restrict__ z,
+                                                        const T* __restrict__ w, EwParams p) {
+  using Tr = OpTraits<OP>;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
+    float xv = 0.f, yv = 0.f, zv = 0.f, wv = 0.f;
+    if constexpr (Tr::uses_x) xv = ldf(x, i);
+    if constexpr (Tr::uses_y) yv = ldf(y, bc_index(p.ymode, i, p.r, p.c));
+    if constexpr (Tr::uses_z) zv = ldf(z, bc_index(p.zmode, i, p.r, p.c));
+    if constexpr (Tr::uses_w) wv = ldf(w, bc_index(p.wmode, i, p.r, p.c));
+    int64_t row = 0, col = 0;
+    if constexpr (Tr::uses_index) { col = i % p.c; row = (i / p.c) % p.r; }
+    stf(out, i, ew_apply<OP>(xv, yv, zv, wv, p.s0, p.s1, row, col));
+  }
+}
+
+// Vector path: every used operand has the output's shape and is 16-byte aligned.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) ew_vec_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                     const T* __restrict__ y, const T* __restrict__ z,
+                                                     const T* __restrict__ w, EwParams p) {
+  using Tr = OpTraits<OP>;
+  constexpr int VN = Vec16<T>::N;
+  const int64_t nvec = p.n / VN;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    float xf[VN], yf[VN], zf[VN], wf[VN], of[VN];
+    Vec16<T> t;
+    if constexpr (Tr::uses_x) { t.load(x + v * VN); t.unpack(xf); }
+    if constexpr (Tr::uses_y) { t.load(y + v * VN); t.unpack(yf); }
+    if constexpr (Tr::uses_z) { t.load(z + v * VN); t.unpack(zf); }
+    if constexpr (Tr::uses_w) { t.load(w + v * VN); t.unpack(wf); }
+#pragma unroll
+    for (int k = 0; k < VN; ++k) {
+      int64_t row = 0, col = 0;
+      if constexpr (Tr::uses_index) { int64_t i = v * VN + k; col = i % p.c; row = (i / p.c) % p.r; }
+      of[k] = ew_apply<OP>(Tr::uses_x ? xf[k] : 0.f, Tr::uses_y ? yf[k] : 0.f, Tr::uses_z ? zf[k] : 0.f,
+                           Tr::uses_w ? wf[k] : 0.f, p.s0, p.s1, row, col);
+    }
+    t.pack(of);
+    t.store(out + v * VN);
+  }
+  // tail
+  const int64_t tail0 = nvec * VN;
+  for (int64_t i = tail0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
+    float xv = 0.f, yv = 0.f, zv = 0.f, wv = 0.f;
+    if constexpr (Tr::uses_x) xv = ldf(x, i);
+    if constexpr (Tr::uses_y) yv = ldf(y, i);
+    if constexpr (Tr::uses_z) zv = ldf(z, i);
+    if constexpr (Tr::uses_w) wv = ldf(w, i);
+    int64_t row = 0, col = 0;
+    if constexpr (Tr::uses_index) { col = i % p.c; row = (i / p.c) % p.r; }
+    stf(out, i, ew_apply<OP>(xv, yv, zv, wv, p.s0, p.s1, row, col));
+  }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int OP>
+int launch_ew(void* out, const void* x, const void* y, const void* z, const void* w, const EwParams& p,
+              cudaStream_t stream) {
+  using Tr = OpTraits<OP>;
+  if (p.n == 0) return DG_OK;
+  if ((Tr::uses_x && !x) || (Tr::uses_y && !y) || (Tr::uses_z && !z) || (Tr::uses_w && !w)) return DG_ERR_BAD_ARG;
+  bool vec = aligned16(out) && (!Tr::uses_x || aligned16(x)) &&
+             (!Tr::uses_y || (p.ymode == DG_BC_SAME && aligned16(y))) &&
+             (!Tr::uses_z || (p.zmode == DG_BC_SAME && aligned16(z))) &&
+             (!Tr::uses_w || (p.wmode == DG_BC_SAME && aligned16(w)));
+  const int threads = 256;
+  if (vec) {
+    int blocks = grid_for(p.n, threads, Vec16<T>::N * 2);
+    ew_vec_kernel<T, OP><<<blocks, threads, 0, stream>>>((T*)out, (const T*)x, (const T*)y, (const T*)z,
+                                                         (const T*)w, p);
+  } else {
+    int blocks = grid_for(p.n, threads, 4);
+    ew_scalar_kernel<T, OP><<<blocks, threads, 0, stream>>>((T*)out, (const T*)x, (const T*)y, (const T*)z,
+                                                            (const T*)w, p);
+  }
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+template <typename T>
+int dispatch_ew(int op, void* out, const void* x, const void* y, const void* z, const void* w,
+                const EwParams& p, cudaStream_t s) {
+  switch (op) {
+#define DG_CASE(OP) case OP: return launch_ew<T, OP>(out, x, y, z, w, p, s);
+    DG_CASE(DG_EW_COPY) DG_CASE(DG_EW_ADD) DG_CASE(DG_EW_SUB) DG_CASE(DG_EW_MUL) DG_CASE(DG_EW_DIV)
+    DG_CASE(DG_EW_ADD_S) DG_CASE(DG_EW_MUL_S) DG_CASE(DG_EW_DIV_S) DG_CASE(DG_EW_RSUB_S)
+    DG_CASE(DG_EW_RDIV_S) DG_CASE(DG_EW_POW_I) DG_CASE(DG_EW_SQRT) DG_CASE(DG_EW_LOG_EPS)
+    DG_CASE(DG_EW_EXP) DG_CASE(DG_EW_RELU) DG_CASE(DG_EW_TANH) DG_CASE(DG_EW_GELU) DG_CASE(DG_EW_NEG)
+    DG_CASE(DG_EW_COPY_Y) DG_CASE(DG_EW_MASK_FILL) DG_CASE(DG_EW_CAUSAL_FILL) DG_CASE(DG_EW_CLAMP)
+    DG_CASE(DG_EW_FMA_S) DG_CASE(DG_EW_DIV_BWD_B) DG_CASE(DG_EW_POW_BWD) DG_CASE(DG_EW_SQRT_BWD)
+    DG_CASE(DG_EW_LOG_BWD) DG_CASE(DG_EW_RDIV_BWD) DG_CASE(DG_EW_RELU_BWD) DG_CASE(DG_EW_TANH_BWD)
+    DG_CASE(DG_EW_GELU_BWD) DG_CASE(DG_EW_MASK_BWD) DG_CASE(DG_EW_CAUSAL_BWD) DG_CASE(DG_EW_VAR_BWD)
+    DG_CASE(DG_EW_STD_BWD) DG_CASE(DG_EW_XENT_PROB_BWD) DG_CASE(DG_EW_MSE_BWD) DG_CASE(DG_EW_SCALE_SHIFT)
+#undef DG_CASE
+  }
+  return DG_ERR_BAD_ARG;
+}
+
+template <typename TO, typename TI>
+__global__ void __launch_bounds__(256) cast_kernel(TO* __restrict__ out, const TI* __restrict__ in, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = Conv<TO>::from_f(Conv<TI>::to_f(in[i]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) accumulate_kernel(T* __restrict__ dst, const T* __restrict__ src, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    stf(dst, i, ldf(dst, i) + ldf(src, i));
+}
+
+}  // namespace dg
+
+extern "C" int dg_elementwise(int op, int dtype, void* out, const void* x, const void* y, const void* z,
+                              const void* w, int ymode, int zmode, int wmode, float s0, float s1,
+                              int64_t n, int64_t r, int64_t c, cudaStream_t stream) {
+  dg::EwParams p{s0, s1, n, r < 1 ? 1 : r, c < 1 ? 1 : c, ymode, zmode, wmode};
+  if (dtype == DG_F32) return dg::dispatch_ew<float>(op, out, x, y, z, w, p, stream);
+  if (dtype == DG_BF16) return dg::dispatch_ew<dg::bf16>(op, out, x, y, z, w, p, stream);
+  return DG_ERR_BAD_ARG;
+}
+
+extern "C" int dg_cast(int out_dtype, void* out, int in_dtype, const void* in, int64_t n, cudaStream_t stream) {
+  if (n == 0) return DG_OK;
+  int blocks = dg::grid_for(n, 256, 4);
+  if (out_dtype == DG_F32 && in_dtype == DG_BF16)
+    dg::cast_kernel<float, dg::bf16><<<blocks, 256, 0, stream>>>((float*)out, (const dg::bf16*)in, n);
+  else if (out_dtype == DG_BF16 && in_dtype == DG_F32)
+    dg::cast_kernel<dg::bf16, float><<<blocks, 256, 0, stream>>>((dg::bf16*)out, (const float*)in, n);
+  else if (out_dtype == DG_F32 && in_dtype == DG_F32)
+    dg::cast_kernel<float, float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)in, n);
+  else if (out_dtype == DG_BF16 && in_dtype == DG_BF16)
+    dg::cast_kernel<dg::bf16, dg::bf16><<<blocks, 256, 0, stream>>>((dg::bf16*)out, (const dg::bf16*)in, n);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_accumulate(int dtype, void* dst, const void* src, int64_t n, cudaStream_t stream) {
+  if (n == 0) return DG_OK;
+  int blocks = dg::grid_for(n, 256, 4);
+  if (dtype == DG_F32)
+    dg::accumulate_kernel<float><<<blocks, 256, 0, stream>>>((float*)dst, (const float*)src, n);
+  else if (dtype == DG_BF16)
+    dg::accumulate_kernel<dg::bf16><<<blocks, 256, 0, stream>>>((dg::bf16*)dst, (const dg::bf16*)src, n);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

@@ -1,0 +1,148 @@
+// Host side of the tcgen05 GEMM: argument validation, TMA tensor-map cache, kernel selection.
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include "gemm_sm100.cuh"
+#include "tma_host.h"
+
+namespace dg {
+namespace sm100 {
+
+template <int BN, int STAGES, bool A_K, bool B_K, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_cta_body<BN, STAGES, A_K, B_K, OutT, false, false>(&tmA, &tmB, p, smem_raw, (int)blockIdx.x, (int)gridDim.x);
+}
+
+struct TmapKey {
+  uint64_t v[8];
+  bool operator==(const TmapKey& o) const { return std::memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct TmapHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 8; ++i) { h ^= k.v[i]; h *= 1099511628211ull; }
+    return (size_t)h;
+  }
+};
+
+static std::mutex g_tmap_mu;
+static std::unordered_map<TmapKey, CUtensorMap, TmapHash> g_tmap_cache;
+
+int get_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ostride,
+             uint64_t bstride, uint32_t box_inner, uint32_t box_outer) {
+  TmapKey k{{(uint64_t)(uintptr_t)base, inner, outer, batch, ostride, bstride, box_inner, box_outer}};
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  auto it = g_tmap_cache.find(k);
+  if (it != g_tmap_cache.end()) { *out = it->second; return 0; }
+  int rc = make_tmap_bf16_3d(out, base, inner, outer, batch, ostride, bstride, box_inner, box_outer);
+  if (rc) return rc;
+  if (g_tmap_cache.size() > 8192) g_tmap_cache.clear();
+  g_tmap_cache.emplace(k, *out);
+  return 0;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// Builds the A and B tensor maps for the chosen operand majors and tile width.
+int build_operand_maps(CUtensorMap* tmA, CUtensorMap* tmB, const dg_gemm_args* a, int BN) {
+  int rc;
+  const int64_t batch = a->batch < 1 ? 1 : a->batch;
+  const int64_t ab = (a->a_bs == 0) ? 1 : batch, bb = (a->b_bs == 0) ? 1 : batch;
+  if (a->a_kmajor) rc = get_tmap(tmA, a->A, a->K, a->M, ab, a->lda, a->a_bs, kBK, kBM);
+  else rc = get_tmap(tmA, a->A, a->M, a->K, ab, a->lda, a->a_bs, 64, kBK);
+  if (rc) return rc;
+  if (a->b_kmajor) rc = get_tmap(tmB, a->B, a->K, a->N, bb, a->ldb, a->b_bs, kBK, BN);
+  else rc = get_tmap(tmB, a->B, a->N, a->K, bb, a->ldb, a->b_bs, 64, kBK);
+  return rc;
+}
+
+void fill_params(GemmParams* p, const dg_gemm_args* a) {
+  std::memset(p, 0, sizeof(*p));
+  p->M = a->M; p->N = a->N; p->K = a->K; p->batch = a->batch < 1 ? 1 : a->batch;
+  p->ldd = a->ldd; p->d_bs = a->d_bs;
+  p->D = a->D; p->bias = a->bias; p->aux = a->aux; p->residual = a->residual;
+  p->bias_dtype = a->bias_dtype; p->epi = a->epi; p->alpha = a->alpha;
+  p->status = a->status;
+  p->a_bcast = (a->a_bs == 0);
+  p->b_bcast = (a->b_bs == 0);
+  p->bias_bs = a->bias_bs;
+}
+
+template <int BN, int STAGES, bool A_K, bool B_K, typename OutT>
+int launch_plain(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using SM = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_K, B_K, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int64_t m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  int64_t tiles = m_tiles * n_tiles * p.batch;
+  int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, kGemmThreads, SM::kTotal, stream>>>(tmA, tmB, p);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+template <int BN, int STAGES>
+int dispatch_layout(const dg_gemm_args* a, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                    cudaStream_t s) {
+  const bool ak = a->a_kmajor != 0, bk = a->b_kmajor != 0, f32 = a->out_dtype == DG_F32;
+#define DG_L(AK, BK)                                                                          \
+  if (ak == AK && bk == BK)                                                                   \
+    return f32 ? launch_plain<BN, STAGES, AK, BK, float>(tmA, tmB, p, s)                      \
+               : launch_plain<BN, STAGES, AK, BK, bf16>(tmA, tmB, p, s);
+  DG_L(true, true) DG_L(true, false) DG_L(false, true) DG_L(false, false)
+#undef DG_L
+  return DG_ERR_BAD_ARG;
+}
+
+}  // namespace sm100
+}  // namespace dg
+
+extern "C" int dg_gemm_sm100_supported(const dg_gemm_args* a) {
+  if (!a || !a->A || !a->B || !a->D) return 0;
+  if (a->M < 1 || a->N < 1 || a->K < 1) return 0;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(a->A) || !al16(a->B)) return 0;
+  if (a->lda % 8 || a->ldb % 8) return 0;
+  if (a->batch > 1 && (a->a_bs % 8 || a->b_bs % 8)) return 0;
+  // the contiguous extent must cover the rows it strides over
+  if (a->a_kmajor ? a->lda < a->K : a->lda < a->M) return 0;
+  if (a->b_kmajor ? a->ldb < a->K : a->ldb < a->N) return 0;
+  if (a->ldd < a->N) return 0;
+  if (a->out_dtype != DG_F32 && a->out_dtype != DG_BF16) return 0;
+  if (a->M > 0x7fffffffLL || a->N > 0x7fffffffLL || a->K > 0x7fffffffLL) return 0;
+  return 1;
+}
+
+extern "C" int dg_gemm_sm100(const dg_gemm_args* a, cudaStream_t stream) {
+  using namespace dg::sm100;
+  if (!dg_gemm_sm100_supported(a)) return DG_ERR_UNSUPPORTED;
+  const int BN = a->N > 128 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc = build_operand_maps(&tmA, &tmB, a, BN);
+  if (rc) return rc;
+  GemmParams p;
+  fill_params(&p, a);
+  if (BN == 256) return dispatch_layout<256, 4>(a, tmA, tmB, p, stream);
+  return dispatch_layout<128, 6>(a, tmA, tmB, p, stream);
+}
+
+extern "C" int dg_version(void) { return 100; }
+extern "C" int dg_device_sm_count(void) { return dg::sm100::sm_count(); }

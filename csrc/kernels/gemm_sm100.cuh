@@ -1,0 +1,426 @@
+// K1/K2: persistent warp-specialised bf16 GEMM on the 5th-generation tensor cores.
+//
+//   D[M,N] = epilogue( alpha * A[M,K] * B[K,N] )          fp32 accumulation in TMEM
+//
+// Structure of one CTA (192 threads, one CTA per SM, static round-robin tile schedule):
+//   warp 0   TMA producer : cp.async.bulk.tensor (128-byte swizzle, no multicast) into a
+//                           STAGES-deep shared-memory ring, mbarrier complete_tx signalling
+//   warp 1   MMA issuer   : one thread issues tcgen05.mma (M=128, N=BN, K=16) x4 per 64-wide
+//                           k block, tcgen05.commit releases the smem stage / publishes the tile
+//   warps 2-5 epilogue    : tcgen05.ld of the fp32 accumulator (double-buffered in TMEM so the
+//                           next tile's main loop overlaps), bias / GELU / dGELU / residual,
+//                           16-byte global stores
+// Operand layouts are chosen per call through the UMMA descriptors (K-major or MN-major for
+// each of A and B), so forward (NN), dgrad (NT) and wgrad (TN) need no transposed copies
+// (reference loops: src/matmul.h:39-79, 158-182; src/linear.h:26).
+//
+// The same kernel body serves the fused collectives through the Comm hooks:
+//   gate_a : the producer waits on a per-row-chunk arrival flag before loading A rows that a
+//            gather role of the same grid copies in from peer GPUs (all-gather -> GEMM)
+//   the epilogue can direct finished tiles to a per-destination base pointer (GEMM -> scatter)
+#pragma once
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dg {
+namespace sm100 {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 8;
+
+struct GemmParams {
+  int64_t M, N, K, batch;
+  int64_t ldd, d_bs;
+  void* D;
+  const void* bias;
+  void* aux;
+  const void* residual;
+  int bias_dtype, epi;
+  float alpha;
+  int* status;
+  int a_bcast, b_bcast;      // operand shared by every batch entry (its tensor map has batch extent 1)
+  int64_t bias_bs;           // element stride of the bias between batch entries (0: shared)
+  // ---- fused-collective hooks (unused by the plain GEMM) ----
+  // all-gather -> GEMM: rows [c*rows_per_chunk, ...) of A may be loaded once a_flags[c] >= a_epoch
+  const int* a_flags;
+  int a_epoch;
+  int64_t rows_per_chunk;
+  int64_t m_tile_rotate;     // tile-row rotation so that locally owned rows are consumed first
+  // GEMM -> scatter: output row block r (of rows_per_dest rows) goes to dest_base[r] + local offset
+  void* const* dest_base;    // device array of per-destination base pointers (null: use D)
+  int64_t rows_per_dest;
+  int* const* dest_flags;    // per-destination flag array; flag[(src_rank * tiles) + tile] = epoch on completion
+  int src_rank;
+  int d_epoch;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void decode_tile(int64_t t, int64_t m_tiles, int64_t n_tiles, int64_t& b, int64_t& mt,
+                                            int64_t& nt) {
+  const int64_t per_batch = m_tiles * n_tiles;
+  b = t / per_batch;
+  int64_t r = t - b * per_batch;
+  const int64_t group_span = (int64_t)kGroupM * n_tiles;
+  const int64_t group = r / group_span;
+  const int64_t first_m = group * kGroupM;
+  int64_t gsz = m_tiles - first_m;
+  if (gsz > kGroupM) gsz = kGroupM;
+  const int64_t in_group = r - group * group_span;
+  mt = first_m + in_group % gsz;
+  nt = in_group / gsz;
+}
+
+template <typename OutT> struct OutVec;
+template <> struct OutVec<bf16> {
+  // 32 fp32 -> 32 bf16 = 64 bytes = 4 x 16 B
+  static __device__ __forceinline__ void store(bf16* dst, const float* v, bool vec_ok, int valid) {
+    if (vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1]);
+        *reinterpret_cast<uint4*>(dst + q * 8) = pk;
+      }
+    } else {
+      for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+    }
+  }
+  static __device__ __forceinline__ void load(const bf16* src, float* v, bool vec_ok, int valid) {
+    if (vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 pk = *reinterpret_cast<const uint4*>(src + q * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 f = __bfloat1622float2(h[e]);
+          v[q * 8 + 2 * e] = f.x; v[q * 8 + 2 * e + 1] = f.y;
+        }
+      }
+    } else {
+      for (int e = 0; e < 32; ++e) v[e] = e < valid ? __bfloat162float(src[e]) : 0.f;
+    }
+  }
+};
+template <> struct OutVec<float> {
+  static __device__ __forceinline__ void store(float* dst, const float* v, bool vec_ok, int valid) {
+    if (vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    } else {
+      for (int e = 0; e < valid; ++e) dst[e] = v[e];
+    }
+  }
+  static __device__ __forceinline__ void load(const float* src, float* v, bool vec_ok, int valid) {
+    if (vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float4 f = *reinterpret_cast<const float4*>(src + q * 4);
+        v[q * 4] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
+      }
+    } else {
+      for (int e = 0; e < 32; ++e) v[e] = e < valid ? src[e] : 0.f;
+    }
+  }
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded spin on a global flag: true when *flag >= epoch.
+__device__ __forceinline__ bool bounded_flag_wait(const int* flag, int epoch, volatile int* abort_flag,
+                                                  long long budget = kWaitCycles) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_sys(flag) >= epoch) return true;
+    __nanosleep(64);
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > budget) return false;
+    }
+  }
+}
+
+// The GEMM roles of one CTA. `cta_rank`/`cta_count` give this CTA's slot among the CTAs that
+// run the GEMM role (fused kernels reserve other CTAs of the grid for copy/reduce roles).
+template <int BN, int STAGES, bool A_KMAJOR, bool B_KMAJOR, typename OutT, bool GATE_A, bool SCATTER_D>
+__device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
+                                              uint8_t* smem_raw, int cta_rank, int cta_count) {
+  using SM = GemmSmem<BN, STAGES>;
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two >= 32");
+  constexpr uint32_t kIdesc = make_idesc_bf16(kBM, BN, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
+
+  // 1024-byte aligned carve-up (128-byte swizzle atoms are 1024 bytes)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * SM::kStageBytes);
+  uint64_t* full_bar = bars;                      // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;            // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;        // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;   // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* never_flag = reinterpret_cast<volatile int*>(tmem_holder + 2);  // stays 0
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    *never_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(tmA);
+    tma_prefetch_desc(tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int64_t m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  const int64_t total_tiles = m_tiles * n_tiles * p.batch;
+  const int64_t k_blocks = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t armed = 0;  // bit s: full_bar[s] armed for a transfer whose completion nobody has observed yet
+      uint32_t armed_parity = 0;
+      for (int64_t t = cta_rank; t < total_tiles && ok; t += cta_count) {
+        int64_t b, mt, nt;
+        decode_tile(t, m_tiles, n_tiles, b, mt, nt);
+        if constexpr (GATE_A) {
+          mt = (mt + p.m_tile_rotate) % m_tiles;
+          // every chunk that overlaps rows [mt*128, mt*128+128) must have arrived
+          const int64_t c0 = (mt * kBM) / p.rows_per_chunk;
+          int64_t last_row = mt * kBM + kBM - 1;
+          if (last_row >= p.M) last_row = p.M - 1;
+          const int64_t c1 = last_row / p.rows_per_chunk;
+          for (int64_t c = c0; c <= c1 && ok; ++c) ok = bounded_flag_wait(p.a_flags + c, p.a_epoch, abort_flag);
+          if (!ok) break;
+          // order the gather role's generic-proxy writes before this thread's async-proxy reads
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        for (int64_t kb = 0; kb < k_blocks; ++kb) {
+          ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+          if (!ok) break;
+          uint8_t* sa = tiles + stage * SM::kStageBytes;
+          uint8_t* sb = sa + SM::kABytes;
+          mbar_expect_tx(&full_bar[stage], SM::kStageBytes);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          const int k0 = (int)(kb * kBK), m0 = (int)(mt * kBM), n0 = (int)(nt * BN);
+          const int za = p.a_bcast ? 0 : (int)b, zb = p.b_bcast ? 0 : (int)b;
+          if constexpr (A_KMAJOR) {
+            tma_load_3d(sa, tmA, &full_bar[stage], k0, m0, za);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c) tma_load_3d(sa + c * 8192, tmA, &full_bar[stage], m0 + c * 64, k0, za);
+          }
+          if constexpr (B_KMAJOR) {
+            tma_load_3d(sb, tmB, &full_bar[stage], k0, n0, zb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * 8192, tmB, &full_bar[stage], n0 + c * 64, k0, zb);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        if (p.status) atomicExch(p.status, 1);
+        *abort_flag = 1;
+        // let copies that are still in flight land before the CTA's shared memory goes away
+        for (int s = 0; s < STAGES; ++s)
+          if (armed & (1u << s)) bounded_wait(&full_bar[s], (armed_parity >> s) & 1u, never_flag, 20000000LL);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int acc = 0;
+      bool ok = true;
+      for (int64_t t = cta_rank; t < total_tiles && ok; t += cta_count) {
+        ok = bounded_wait(&tempty_bar[acc], acc_phase[acc] ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int64_t kb = 0; kb < k_blocks; ++kb) {
+          ok = bounded_wait(&full_bar[stage], phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * SM::kStageBytes);
+          const uint32_t sb = sa + SM::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            uint64_t da, db;
+            if constexpr (A_KMAJOR) da = make_smem_desc(sa + k * 32, 16, 1024);
+            else da = make_smem_desc(sa + k * 2048, 8192, 1024);
+            if constexpr (B_KMAJOR) db = make_smem_desc(sb + k * 32, 16, 1024);
+            else db = make_smem_desc(sb + k * 2048, 8192, 1024);
+            umma_f16(tmem_d, da, db, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // smem stage reusable once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);      // accumulator complete
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+      }
+      if (!ok) {
+        if (p.status) atomicExch(p.status, 2);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_group = warp & 3;  // TMEM sub-partition this warp may read
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    bool ok = true;
+    const bool d_vec_base = ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) && ((p.ldd * sizeof(OutT)) % 16 == 0) &&
+                            ((p.d_bs * sizeof(OutT)) % 16 == 0);
+    for (int64_t t = cta_rank; t < total_tiles; t += cta_count) {
+      int64_t b, mt, nt;
+      decode_tile(t, m_tiles, n_tiles, b, mt, nt);
+      if constexpr (GATE_A) mt = (mt + p.m_tile_rotate) % m_tiles;
+      ok = bounded_wait(&tfull_bar[acc], acc_phase[acc], abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = mt * kBM + lane_group * 32 + lane;
+      const bool row_ok = row < p.M;
+      OutT* drow;
+      if constexpr (SCATTER_D) {
+        const int64_t dest = row_ok ? row / p.rows_per_dest : 0;
+        const int64_t lrow = row - dest * p.rows_per_dest;
+        drow = reinterpret_cast<OutT*>(p.dest_base[dest]) + lrow * p.ldd;
+      } else {
+        drow = reinterpret_cast<OutT*>(p.D) + b * p.d_bs + row * p.ldd;
+      }
+      const bf16* auxrow = p.aux ? reinterpret_cast<const bf16*>(p.aux) + b * p.d_bs + row * p.ldd : nullptr;
+      const OutT* resrow = p.residual ? reinterpret_cast<const OutT*>(p.residual) + b * p.d_bs + row * p.ldd : nullptr;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int64_t col0 = nt * BN + ch * 32;
+        uint32_t raw[32];
+        const uint32_t taddr = tmem_base + (uint32_t)(acc * BN + ch * 32) + ((uint32_t)(lane_group * 32) << 16);
+        tmem_ld_32x32(taddr, raw);
+        tc_wait_ld();
+        if (ch == BN / 32 - 1) {
+          // accumulator fully read: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        if (col0 >= p.N || !row_ok) continue;
+        int valid = (int)((p.N - col0) < 32 ? (p.N - col0) : 32);
+        const bool vec_ok = d_vec_base && valid == 32;
+        float v[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
+        if (p.bias) {
+          if (p.bias_dtype == DG_BF16) {
+            const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + b * p.bias_bs + col0;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += __bfloat162float(bp[e]);
+          } else {
+            const float* bp = reinterpret_cast<const float*>(p.bias) + b * p.bias_bs + col0;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += bp[e];
+          }
+        }
+        if (p.epi == DG_EPI_GELU || p.epi == DG_EPI_RELU) {
+          if (p.aux) OutVec<bf16>::store(reinterpret_cast<bf16*>(p.aux) + b * p.d_bs + row * p.ldd + col0, v,
+                                         vec_ok && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
+          if (p.epi == DG_EPI_GELU) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = gelu_f(v[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = v[e] > 0.f ? v[e] : 0.f;
+          }
+        } else if (p.epi == DG_EPI_DGELU || p.epi == DG_EPI_DRELU) {
+          float a[32];
+          OutVec<bf16>::load(auxrow + col0, a, vec_ok && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
+          if (p.epi == DG_EPI_DGELU) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] *= gelu_grad_f(a[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = a[e] > 0.f ? v[e] : 0.f;
+          }
+        }
+        if (resrow) {
+          float r[32];
+          OutVec<OutT>::load(resrow + col0, r, vec_ok && ((reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0), valid);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] += r[e];
+        }
+        OutVec<OutT>::store(drow + col0, v, vec_ok, valid);
+      }
+      if constexpr (SCATTER_D) {
+        // publish the tile to its destination: all four epilogue warps have stored their rows
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int64_t dest = (mt * kBM) / p.rows_per_dest;
+          const int64_t tiles_per_dest = (p.rows_per_dest / kBM) * n_tiles;
+          const int64_t ltile = (mt - dest * (p.rows_per_dest / kBM)) * n_tiles + nt;
+          st_release_sys(p.dest_flags[dest] + (int64_t)p.src_rank * tiles_per_dest + ltile, p.d_epoch);
+        }
+      }
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+    if (!ok && lane == 0) {
+      if (p.status) atomicExch(p.status, 3);
+      *abort_flag = 1;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace sm100
+}  // namespace dg

@@ -1,0 +1,116 @@
+// K11: fused optimizers. Single-tensor and multi-tensor Adam/AdamW and SGD on an fp32
+// master copy with an optional low-precision (bf16) shadow parameter written in the same pass.
+// Update rule and defaults follow the reference (src/optimizers.h:32-59): bias-corrected
+// moments, p -= lr * mhat / (sqrt(vhat) + eps), one step counter per tensor. Weight decay is
+// decoupled (AdamW) and off when wd == 0, which reproduces the reference exactly.
+#include "common.cuh"
+
+namespace dg {
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, wd, grad_scale;
+};
+
+__device__ __forceinline__ float adam_update(float p, float g, float& m, float& v, const AdamHyper& h, float bc1,
+                                             float bc2) {
+  g *= h.grad_scale;
+  m = h.beta1 * m + (1.f - h.beta1) * g;
+  v = h.beta2 * v + (1.f - h.beta2) * g * g;
+  float mhat = m / bc1, vhat = v / bc2;
+  p -= h.lr * (mhat / (sqrtf(vhat) + h.eps) + h.wd * p);
+  return p;
+}
+
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256) adam_kernel(TP* __restrict__ p, float* __restrict__ master,
+                                                   const TG* __restrict__ g, float* __restrict__ m,
+                                                   float* __restrict__ v, int64_t n, AdamHyper h, float bc1, float bc2) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float pv = master ? master[i] : Conv<TP>::to_f(p[i]);
+    float mv = m[i], vv = v[i];
+    pv = adam_update(pv, Conv<TG>::to_f(g[i]), mv, vv, h, bc1, bc2);
+    m[i] = mv; v[i] = vv;
+    if (master) master[i] = pv;
+    p[i] = Conv<TP>::from_f(pv);
+  }
+}
+
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256) sgd_kernel(TP* __restrict__ p, float* __restrict__ master,
+                                                  const TG* __restrict__ g, int64_t n, float lr, float grad_scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float pv = master ? master[i] : Conv<TP>::to_f(p[i]);
+    pv -= lr * grad_scale * Conv<TG>::to_f(g[i]);
+    if (master) master[i] = pv;
+    p[i] = Conv<TP>::from_f(pv);
+  }
+}
+
+// Multi-tensor: chunk list entries are (record index, element offset); one CTA per chunk.
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256) adam_multi_kernel(const dg_adam_rec* __restrict__ recs,
+                                                         const int64_t* __restrict__ chunks, int64_t chunk_elems,
+                                                         AdamHyper h) {
+  const int64_t rec_i = chunks[2 * (int64_t)blockIdx.x], off = chunks[2 * (int64_t)blockIdx.x + 1];
+  const dg_adam_rec r = recs[rec_i];
+  int64_t hi = off + chunk_elems;
+  if (hi > r.n) hi = r.n;
+  const float bc1 = 1.f - powf(h.beta1, (float)r.step), bc2 = 1.f - powf(h.beta2, (float)r.step);
+  TP* p = (TP*)r.p;
+  const TG* g = (const TG*)r.g;
+  for (int64_t i = off + threadIdx.x; i < hi; i += blockDim.x) {
+    float pv = r.master ? r.master[i] : Conv<TP>::to_f(p[i]);
+    float mv = r.m[i], vv = r.v[i];
+    pv = adam_update(pv, Conv<TG>::to_f(g[i]), mv, vv, h, bc1, bc2);
+    r.m[i] = mv; r.v[i] = vv;
+    if (r.master) r.master[i] = pv;
+    p[i] = Conv<TP>::from_f(pv);
+  }
+}
+
+}  // namespace dg
+
+#define DG_DISPATCH_PG(PD, GD, CALL)                                        \
+  if ((PD) == DG_F32 && (GD) == DG_F32) { using TP = float; using TG = float; CALL; }                 \
+  else if ((PD) == DG_F32 && (GD) == DG_BF16) { using TP = float; using TG = dg::bf16; CALL; }        \
+  else if ((PD) == DG_BF16 && (GD) == DG_BF16) { using TP = dg::bf16; using TG = dg::bf16; CALL; }    \
+  else if ((PD) == DG_BF16 && (GD) == DG_F32) { using TP = dg::bf16; using TG = float; CALL; }        \
+  else return DG_ERR_BAD_ARG;
+
+extern "C" int dg_adam_step(int p_dtype, void* p, float* master, int g_dtype, const void* g, float* m, float* v,
+                            int64_t n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                            float grad_scale, cudaStream_t stream) {
+  if (n == 0) return DG_OK;
+  if (step < 1) return DG_ERR_BAD_ARG;
+  dg::AdamHyper h{lr, beta1, beta2, eps, wd, grad_scale};
+  float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  int blocks = dg::grid_for(n, 256, 4);
+  DG_DISPATCH_PG(p_dtype, g_dtype,
+                 (dg::adam_kernel<TP, TG><<<blocks, 256, 0, stream>>>((TP*)p, master, (const TG*)g, m, v, n, h, bc1, bc2)));
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_sgd_step(int p_dtype, void* p, float* master, int g_dtype, const void* g, int64_t n, float lr,
+                           float grad_scale, cudaStream_t stream) {
+  if (n == 0) return DG_OK;
+  int blocks = dg::grid_for(n, 256, 4);
+  DG_DISPATCH_PG(p_dtype, g_dtype,
+                 (dg::sgd_kernel<TP, TG><<<blocks, 256, 0, stream>>>((TP*)p, master, (const TG*)g, n, lr, grad_scale)));
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_adam_multi(int p_dtype, int g_dtype, const dg_adam_rec* recs_dev, const int64_t* chunk_dev,
+                             int64_t n_chunks, int64_t chunk_elems, float lr, float beta1, float beta2, float eps,
+                             float wd, float grad_scale, cudaStream_t stream) {
+  if (n_chunks == 0) return DG_OK;
+  if (n_chunks > 0x7fffffff || chunk_elems <= 0) return DG_ERR_BAD_ARG;
+  dg::AdamHyper h{lr, beta1, beta2, eps, wd, grad_scale};
+  DG_DISPATCH_PG(p_dtype, g_dtype,
+                 (dg::adam_multi_kernel<TP, TG><<<(unsigned)n_chunks, 256, 0, stream>>>(recs_dev, chunk_dev, chunk_elems, h)));
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

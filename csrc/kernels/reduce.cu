@@ -1,0 +1,205 @@
+// K9: reductions with fp32 accumulation and a fixed (deterministic) summation order.
+//   rows : x[R, C]    -> out[R]       one warp per row, two passes for var/std
+//   cols : x[B, R, C] -> out[B, C]    two-stage: per-split partial sums in scratch, then a fold
+//   all  : x[n]       -> out[1]       two-stage through scratch
+// Covers simple_sum / sum / mean / var / std_dev and the broadcast-gradient reductions of the
+// reference (src/ops.h:366-385, src/sum.h, src/mean.h, src/var.h, src/std.h,
+// src/broadcasting.h:106-119).
+#include "common.cuh"
+
+namespace dg {
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(T* __restrict__ out, T* __restrict__ mean_out,
+                                                          const T* __restrict__ x, int64_t R, int64_t C,
+                                                          int mode) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp; row < R; row += nwarps) {
+    const T* p = x + row * C;
+    float s = 0.f;
+    for (int64_t j = lane; j < C; j += 32) s += ldf(p, j);
+    s = warp_sum(s);
+    float res = s;
+    if (mode != DG_RED_SUM) {
+      float mu = s / (float)C;
+      res = mu;
+      if (mode >= DG_RED_VAR) {
+        float q = 0.f;
+        for (int64_t j = lane; j < C; j += 32) { float d = ldf(p, j) - mu; q += d * d; }
+        q = warp_sum(q) / (float)C;
+        res = (mode == DG_RED_STD) ? sqrtf(q) : q;
+        if (mean_out && lane == 0) stf(mean_out, row, mu);
+      }
+    }
+    if (lane == 0) stf(out, row, res);
+  }
+}
+
+// Stage 1 of the column reduction: partial[b, s, c] = sum over the split's rows of (x - shift)^pw.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_partial_kernel(float* __restrict__ partial,
+                                                                  const T* __restrict__ x,
+                                                                  const float* __restrict__ shift, int64_t R,
+                                                                  int64_t C, int64_t rows_per_split, int S,
+                                                                  int square) {
+  __shared__ float sh[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z, s = blockIdx.y;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+  const int64_t r0 = s * rows_per_split;
+  int64_t r1 = r0 + rows_per_split;
+  if (r1 > R) r1 = R;
+  float acc = 0.f;
+  if (c < C) {
+    const float sv = shift ? shift[b * C + c] : 0.f;
+    const T* p = x + b * R * C + c;
+    for (int64_t r = r0 + ty; r < r1; r += 8) {
+      float v = ldf(p, r * C) - sv;
+      acc += square ? v * v : v;
+    }
+  }
+  sh[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][tx];
+    partial[(b * S + s) * C + c] = t;
+  }
+}
+
+// Stage 2: fold the S partials. post: 0 -> scale*sum into T out; 1 -> sqrt(scale*sum); also optional fp32 copy.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_fold_kernel(T* __restrict__ out, float* __restrict__ out_f32,
+                                                               const float* __restrict__ partial, int64_t BC,
+                                                               int64_t C, int S, float scale, int do_sqrt) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < BC; i += stride) {
+    const int64_t b = i / C, c = i - b * C;
+    float t = 0.f;
+    for (int s = 0; s < S; ++s) t += partial[(b * S + s) * C + c];
+    t *= scale;
+    if (do_sqrt) t = sqrtf(t);
+    if (out) stf(out, i, t);
+    if (out_f32) out_f32[i] = t;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sum_all_partial_kernel(float* __restrict__ partial, const T* __restrict__ x,
+                                                              int64_t n, int64_t chunk) {
+  __shared__ float sh[33];
+  const int64_t lo = (int64_t)blockIdx.x * chunk;
+  int64_t hi = lo + chunk;
+  if (hi > n) hi = n;
+  float acc = 0.f;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) acc += ldf(x, i);
+  acc = block_sum(acc, sh);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sum_all_fold_kernel(T* __restrict__ out, const float* __restrict__ partial,
+                                                           int nparts, float scale) {
+  __shared__ float sh[33];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partial[i];
+  acc = block_sum(acc, sh);
+  if (threadIdx.x == 0) stf(out, 0, acc * scale);
+}
+
+static inline int cols_splits(int64_t B, int64_t R, int64_t C) {
+  int64_t col_blocks = (C + 31) / 32;
+  int64_t want = (148 * 4 + B * col_blocks - 1) / (B * col_blocks);
+  int64_t max_s = (R + 63) / 64;
+  if (want > max_s) want = max_s;
+  if (want < 1) want = 1;
+  if (want > 256) want = 256;
+  return (int)want;
+}
+
+template <typename T>
+int launch_reduce_cols(void* out, void* mean_out, const void* x, int64_t B, int64_t R, int64_t C, int mode,
+                       void* scratch, cudaStream_t stream) {
+  const int S = cols_splits(B, R, C);
+  const int64_t rps = (R + S - 1) / S;
+  float* mean_f = (float*)scratch;
+  float* partial = mean_f + B * C;
+  dim3 grid((unsigned)((C + 31) / 32), (unsigned)S, (unsigned)B);
+  const int fold_blocks = grid_for(B * C, 256);
+  reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, nullptr, R, C, rps, S, 0);
+  DG_CHECK_LAUNCH();
+  if (mode == DG_RED_SUM || mode == DG_RED_MEAN) {
+    float scale = mode == DG_RED_SUM ? 1.f : 1.f / (float)R;
+    reduce_cols_fold_kernel<T><<<fold_blocks, 256, 0, stream>>>((T*)out, nullptr, partial, B * C, C, S, scale, 0);
+    DG_CHECK_LAUNCH();
+    return DG_OK;
+  }
+  reduce_cols_fold_kernel<T><<<fold_blocks, 256, 0, stream>>>((T*)mean_out, mean_f, partial, B * C, C, S,
+                                                              1.f / (float)R, 0);
+  DG_CHECK_LAUNCH();
+  reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, mean_f, R, C, rps, S, 1);
+  DG_CHECK_LAUNCH();
+  reduce_cols_fold_kernel<T><<<fold_blocks, 256, 0, stream>>>((T*)out, nullptr, partial, B * C, C, S,
+                                                              1.f / (float)R, mode == DG_RED_STD ? 1 : 0);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+}  // namespace dg
+
+extern "C" int dg_reduce_rows(int dtype, void* out, void* mean_out, const void* x, int64_t R, int64_t C,
+                              int mode, cudaStream_t stream) {
+  if (R == 0) return DG_OK;
+  if (C <= 0 || mode < 0 || mode > 3) return DG_ERR_BAD_ARG;
+  int blocks = dg::grid_for(R, 8);  // 8 warps (rows) per block
+  if (dtype == DG_F32)
+    dg::reduce_rows_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (float*)mean_out, (const float*)x, R, C, mode);
+  else if (dtype == DG_BF16)
+    dg::reduce_rows_kernel<dg::bf16><<<blocks, 256, 0, stream>>>((dg::bf16*)out, (dg::bf16*)mean_out,
+                                                               (const dg::bf16*)x, R, C, mode);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int64_t dg_reduce_cols_scratch_bytes(int64_t B, int64_t R, int64_t C) {
+  if (B <= 0 || R <= 0 || C <= 0) return 0;
+  return (int64_t)sizeof(float) * (B * C + B * C * (int64_t)dg::cols_splits(B, R, C));
+}
+
+extern "C" int dg_reduce_cols(int dtype, void* out, void* mean_out, const void* x, int64_t B, int64_t R,
+                              int64_t C, int mode, void* scratch, cudaStream_t stream) {
+  if (B == 0 || C == 0) return DG_OK;
+  if (R <= 0 || mode < 0 || mode > 3 || !scratch) return DG_ERR_BAD_ARG;
+  if (B > 65535) return DG_ERR_TOO_LARGE;
+  if (dtype == DG_F32) return dg::launch_reduce_cols<float>(out, mean_out, x, B, R, C, mode, scratch, stream);
+  if (dtype == DG_BF16) return dg::launch_reduce_cols<dg::bf16>(out, mean_out, x, B, R, C, mode, scratch, stream);
+  return DG_ERR_BAD_ARG;
+}
+
+extern "C" int dg_sum_all(int dtype, void* out, const void* x, int64_t n, float scale, void* scratch,
+                          cudaStream_t stream) {
+  if (n <= 0 || !scratch) return DG_ERR_BAD_ARG;
+  int64_t parts = (n + 8191) / 8192;
+  if (parts > 1024) parts = 1024;
+  int64_t chunk = (n + parts - 1) / parts;
+  parts = (n + chunk - 1) / chunk;
+  float* partial = (float*)scratch;
+  if (dtype == DG_F32) {
+    dg::sum_all_partial_kernel<float><<<(int)parts, 256, 0, stream>>>(partial, (const float*)x, n, chunk);
+    DG_CHECK_LAUNCH();
+    dg::sum_all_fold_kernel<float><<<1, 256, 0, stream>>>((float*)out, partial, (int)parts, scale);
+  } else if (dtype == DG_BF16) {
+    dg::sum_all_partial_kernel<dg::bf16><<<(int)parts, 256, 0, stream>>>(partial, (const dg::bf16*)x, n, chunk);
+    DG_CHECK_LAUNCH();
+    dg::sum_all_fold_kernel<dg::bf16><<<1, 256, 0, stream>>>((dg::bf16*)out, partial, (int)parts, scale);
+  } else {
+    return DG_ERR_BAD_ARG;
+  }
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

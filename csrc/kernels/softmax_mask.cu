@@ -1,0 +1,110 @@
+// K5: fused (scale * x) -> mask -> softmax over the last dim, forward and backward.
+// Mask semantics follow the reference: a masked logit is REPLACED by -1e9 before the
+// max-subtracted softmax (src/masking.h:45-54, 102-111; src/softmax.h:50-70), and receives
+// zero gradient. One CTA per row; the row is held in registers when it fits, re-read from
+// L1/L2 otherwise.
+#include "common.cuh"
+
+namespace dg {
+
+constexpr float kMaskFill = -1e9f;
+
+template <typename T>
+__device__ __forceinline__ float masked_logit(const T* xr, const T* mr, int mask_mode, float scale, int64_t i,
+                                              int64_t j) {
+  float v = ldf(xr, j) * scale;
+  if (mask_mode == 1) { if (j > i) v = kMaskFill; }
+  else if (mask_mode == 2) { if (ldf(mr, j) == 0.f) v = kMaskFill; }
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                          const T* __restrict__ mask, int mask_mode, float scale,
+                                                          int64_t rows, int64_t r, int64_t c) {
+  __shared__ float sh[33];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * c;
+    const T* mr = mask ? mask + row * c : nullptr;
+    T* orow = out + row * c;
+    const int64_t i = row % r;
+    float mx = -INFINITY;
+    for (int64_t j = threadIdx.x; j < c; j += blockDim.x)
+      mx = fmaxf(mx, masked_logit(xr, mr, mask_mode, scale, i, j));
+    mx = block_max(mx, sh);
+    float s = 0.f;
+    for (int64_t j = threadIdx.x; j < c; j += blockDim.x)
+      s += __expf(masked_logit(xr, mr, mask_mode, scale, i, j) - mx);
+    s = block_sum(s, sh);
+    const float inv = 1.f / s;
+    for (int64_t j = threadIdx.x; j < c; j += blockDim.x)
+      stf(orow, j, __expf(masked_logit(xr, mr, mask_mode, scale, i, j) - mx) * inv);
+  }
+}
+
+// gx = scale * s * (g - sum_j g_j s_j), zero at masked positions.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(T* __restrict__ gx, const T* __restrict__ g,
+                                                          const T* __restrict__ s, const T* __restrict__ mask,
+                                                          int mask_mode, float scale, int64_t rows, int64_t r,
+                                                          int64_t c) {
+  __shared__ float sh[33];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* gr = g + row * c;
+    const T* sr = s + row * c;
+    const T* mr = mask ? mask + row * c : nullptr;
+    T* o = gx + row * c;
+    const int64_t i = row % r;
+    float dot = 0.f;
+    for (int64_t j = threadIdx.x; j < c; j += blockDim.x) dot += ldf(gr, j) * ldf(sr, j);
+    dot = block_sum(dot, sh);
+    for (int64_t j = threadIdx.x; j < c; j += blockDim.x) {
+      float v = scale * ldf(sr, j) * (ldf(gr, j) - dot);
+      if (mask_mode == 1 && j > i) v = 0.f;
+      if (mask_mode == 2 && ldf(mr, j) == 0.f) v = 0.f;
+      stf(o, j, v);
+    }
+  }
+}
+
+}  // namespace dg
+
+extern "C" int dg_softmax_fwd(int dtype, void* out, const void* x, const void* mask, int mask_mode, float scale,
+                              int64_t rows, int64_t r, int64_t c, cudaStream_t stream) {
+  if (rows == 0 || c == 0) return DG_OK;
+  if (mask_mode == 2 && !mask) return DG_ERR_BAD_ARG;
+  if (r < 1) r = 1;
+  int blocks = (int)(rows < 148 * 32 ? rows : 148 * 32);
+  int threads = c >= 1024 ? 256 : (c >= 256 ? 128 : 64);
+  if (dtype == DG_F32)
+    dg::softmax_fwd_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)x, (const float*)mask,
+                                                                  mask_mode, scale, rows, r, c);
+  else if (dtype == DG_BF16)
+    dg::softmax_fwd_kernel<dg::bf16><<<blocks, threads, 0, stream>>>((dg::bf16*)out, (const dg::bf16*)x,
+                                                                     (const dg::bf16*)mask, mask_mode, scale, rows, r, c);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_softmax_bwd(int dtype, void* gx, const void* g, const void* out, const void* mask,
+                              int mask_mode, float scale, int64_t rows, int64_t r, int64_t c,
+                              cudaStream_t stream) {
+  if (rows == 0 || c == 0) return DG_OK;
+  if (mask_mode == 2 && !mask) return DG_ERR_BAD_ARG;
+  if (r < 1) r = 1;
+  int blocks = (int)(rows < 148 * 32 ? rows : 148 * 32);
+  int threads = c >= 1024 ? 256 : (c >= 256 ? 128 : 64);
+  if (dtype == DG_F32)
+    dg::softmax_bwd_kernel<float><<<blocks, threads, 0, stream>>>((float*)gx, (const float*)g, (const float*)out,
+                                                                  (const float*)mask, mask_mode, scale, rows, r, c);
+  else if (dtype == DG_BF16)
+    dg::softmax_bwd_kernel<dg::bf16><<<blocks, threads, 0, stream>>>((dg::bf16*)gx, (const dg::bf16*)g,
+                                                                     (const dg::bf16*)out, (const dg::bf16*)mask,
+                                                                     mask_mode, scale, rows, r, c);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

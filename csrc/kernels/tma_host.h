@@ -1,0 +1,46 @@
+// Host-side helper that builds TMA tensor maps (cuTensorMapEncodeTiled) without linking
+// libcuda: the driver entry point is fetched through the runtime at first use, so the library
+// also loads on machines that have no driver (build checks on CPU-only hosts).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+namespace dg {
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
+// bf16 3-D map {inner, outer, batch} with a {box_inner, box_outer, 1} box and 128-byte swizzle.
+// Strides are in elements. Returns 0 on success.
+inline int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t batch,
+                             uint64_t outer_stride, uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -3;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {outer_stride * 2, batch_stride * 2};
+  if (batch <= 1) strides[1] = outer_stride * 2 * outer;
+  if (strides[1] == 0) strides[1] = 16;
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+}  // namespace dg

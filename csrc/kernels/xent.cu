@@ -1,0 +1,121 @@
+// K7: fused softmax-cross-entropy on logits with integer targets. One CTA per row:
+// pass 1 keeps a running (max, sum-exp) pair per thread and merges them, pass 2 writes
+// dlogits = (softmax - onehot) * grad_scale, in place if asked. Replaces the reference's
+// softmax -> cross_entropy-on-probabilities chain (src/softmax.h:40-79, src/loss.h:27-52)
+// without its missing-eps hazard; 64-bit indexing throughout (tokens * vocab exceeds 2^31).
+#include "common.cuh"
+
+namespace dg {
+
+__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
+  float mm = fmaxf(m, m2);
+  if (mm == -INFINITY) { m = mm; s = 0.f; return; }
+  s = s * __expf(m - mm) + s2 * __expf(m2 - mm);
+  m = mm;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) xent_kernel(float* __restrict__ loss_rows, float* __restrict__ lse_out,
+                                                   T* dlogits, const T* logits,
+                                                   const int64_t* __restrict__ target, int64_t T_rows, int64_t V,
+                                                   int64_t ld, float grad_scale, bool vec) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float shm[32], shs[32];
+  __shared__ float bc[2];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int64_t row = blockIdx.x; row < T_rows; row += gridDim.x) {
+    const T* xr = logits + row * ld;
+    const int64_t tgt = target[row];
+    // read the target logit before anything is overwritten (dlogits may alias logits)
+    float tgt_logit = 0.f;
+    if (threadIdx.x == 0 && tgt >= 0 && tgt < V) tgt_logit = ldf(xr, tgt);
+    float m = -INFINITY, s = 0.f;
+    if (vec) {
+      for (int64_t v = threadIdx.x; v < V / VN; v += blockDim.x) {
+        Vec16<T> t; t.load(xr + v * VN);
+        float f[VN]; t.unpack(f);
+        float lm = f[0];
+#pragma unroll
+        for (int e = 1; e < VN; ++e) lm = fmaxf(lm, f[e]);
+        float ls = 0.f;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) ls += __expf(f[e] - lm);
+        online_merge(m, s, lm, ls);
+      }
+    } else {
+      for (int64_t j = threadIdx.x; j < V; j += blockDim.x) online_merge(m, s, ldf(xr, j), 1.f);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      online_merge(m, s, m2, s2);
+    }
+    __syncthreads();
+    if (lane == 0) { shm[wid] = m; shs[wid] = s; }
+    __syncthreads();
+    if (wid == 0) {
+      float mm = lane < nw ? shm[lane] : -INFINITY, ss = lane < nw ? shs[lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float m2 = __shfl_xor_sync(0xffffffffu, mm, o), s2 = __shfl_xor_sync(0xffffffffu, ss, o);
+        online_merge(mm, ss, m2, s2);
+      }
+      if (lane == 0) { bc[0] = mm; bc[1] = ss; }
+    }
+    __syncthreads();
+    const float mx = bc[0], sum = bc[1];
+    const float lse = mx + logf(sum);
+    if (threadIdx.x == 0) {
+      float tl = (tgt >= 0 && tgt < V) ? tgt_logit : lse;
+      loss_rows[row] = lse - tl;
+      if (lse_out) lse_out[row] = lse;
+    }
+    if (dlogits) {
+      T* dr = dlogits + row * ld;
+      if (vec) {
+        for (int64_t v = threadIdx.x; v < V / VN; v += blockDim.x) {
+          Vec16<T> t; t.load(xr + v * VN);
+          float f[VN]; t.unpack(f);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) {
+            float p = __expf(f[e] - lse);
+            if (v * VN + e == tgt) p -= 1.f;
+            f[e] = p * grad_scale;
+          }
+          t.pack(f); t.store(dr + v * VN);
+        }
+      } else {
+        for (int64_t j = threadIdx.x; j < V; j += blockDim.x) {
+          float p = __expf(ldf(xr, j) - lse);
+          if (j == tgt) p -= 1.f;
+          stf(dr, j, p * grad_scale);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace dg
+
+extern "C" int dg_xent_fwd_bwd(int dtype, float* loss_rows, float* lse, void* dlogits, const void* logits,
+                               const int64_t* target, int64_t T, int64_t V, int64_t ld, float grad_scale,
+                               cudaStream_t stream) {
+  if (T == 0) return DG_OK;
+  if (V <= 0 || ld < V) return DG_ERR_BAD_ARG;
+  int blocks = (int)(T < 148 * 16 ? T : 148 * 16);
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (dtype == DG_F32) {
+    bool vec = (V % 4 == 0) && (ld % 4 == 0) && al(logits) && (!dlogits || al(dlogits));
+    dg::xent_kernel<float><<<blocks, 256, 0, stream>>>(loss_rows, lse, (float*)dlogits, (const float*)logits, target,
+                                                       T, V, ld, grad_scale, vec);
+  } else if (dtype == DG_BF16) {
+    bool vec = (V % 8 == 0) && (ld % 8 == 0) && al(logits) && (!dlogits || al(dlogits));
+    dg::xent_kernel<dg::bf16><<<blocks, 256, 0, stream>>>(loss_rows, lse, (dg::bf16*)dlogits, (const dg::bf16*)logits,
+                                                          target, T, V, ld, grad_scale, vec);
+  } else {
+    return DG_ERR_BAD_ARG;
+  }
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

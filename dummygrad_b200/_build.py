@@ -1,0 +1,115 @@
+"""In-tree build of the native libraries (sm_100a only).
+
+``build_all()`` compiles every ``csrc/**/*.cu`` with
+``nvcc -gencode arch=compute_100a,code=sm_100a -lineinfo`` into one shared library,
+``dummygrad_b200/lib/libdgb200.so`` (C ABI, statically linked CUDA runtime, no libcuda link
+dependency), plus the host-only C++ runtime ``libdgcore.so``. nvcc cross-compiles, so this
+works on hosts without a GPU. Objects are rebuilt only when a source or header is newer.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+LIBDIR = Path(__file__).resolve().parent / "lib"
+OBJDIR = ROOT / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=default",
+    "--expt-relaxed-constexpr",
+    "-diag-suppress", "177,550",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; the sm_100a kernels cannot be built")
+
+
+def _headers_mtime() -> float:
+    newest = 0.0
+    for ext in ("*.h", "*.cuh", "*.hpp"):
+        for p in CSRC.rglob(ext):
+            newest = max(newest, p.stat().st_mtime)
+    return newest
+
+
+def cuda_sources() -> list[Path]:
+    return sorted(list((CSRC / "kernels").glob("*.cu")) + list((CSRC / "comm").glob("*.cu")))
+
+
+def _compile_one(src: Path, hdr_mtime: float, verbose: bool, extra: list[str]) -> Path:
+    obj = OBJDIR / (src.parent.name + "_" + src.stem + ".o")
+    if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
+        return obj
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(CSRC / "include"), "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr.strip():
+        print(r.stderr, flush=True)
+    return obj
+
+
+def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile all CUDA sources and link ``libdgb200.so``. Returns its path."""
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    out = LIBDIR / "libdgb200.so"
+    srcs = cuda_sources()
+    hdr_mtime = _headers_mtime()
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(lambda s: _compile_one(s, hdr_mtime, verbose or ptxas_info, extra), srcs))
+    if out.exists() and all(out.stat().st_mtime > o.stat().st_mtime for o in objs):
+        return out
+    cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(out),
+           *[str(o) for o in objs], "-lpthread", "-ldl"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+def build_core(verbose: bool = False) -> Path | None:
+    """Build the host C++ runtime (engine, launcher helpers) if its sources exist."""
+    srcs = sorted((CSRC / "core").glob("*.cc"))
+    if not srcs:
+        return None
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    out = LIBDIR / "libdgcore.so"
+    newest = max([s.stat().st_mtime for s in srcs] + [_headers_mtime()])
+    if out.exists() and out.stat().st_mtime > newest:
+        return out
+    cmd = ["g++", "-O2", "-std=c++20", "-fPIC", "-shared", "-pthread", "-I", str(CSRC / "include"),
+           "-I", str(CSRC / "core"), *[str(s) for s in srcs], "-o", str(out)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+def build_all(verbose: bool = False) -> None:
+    build_kernels(verbose=verbose)
+    build_core(verbose=verbose)
+
+
+if __name__ == "__main__":
+    build_kernels(verbose=True, ptxas_info="--ptxas" in sys.argv)
+    build_core(verbose=True)
+    print("built:", *(str(p) for p in LIBDIR.glob("*.so")))

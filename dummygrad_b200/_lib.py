@@ -1,0 +1,176 @@
+"""ctypes binding of ``libdgb200.so`` (the hand-written sm_100a kernel library).
+
+The library is built in-tree by :mod:`dummygrad_b200._build` and loaded lazily. On a machine
+with a GPU a missing or unloadable library is a hard error: no op silently falls back to
+PyTorch math on CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libdgb200.so"
+
+F32, BF16 = 0, 1
+
+# broadcast modes (csrc/include/dgb200.h)
+BC_SAME, BC_ROW, BC_COL, BC_SCALAR, BC_MAT, BC_ROWS, BC_COLS = range(7)
+
+_EW_NAMES = [
+    "COPY", "ADD", "SUB", "MUL", "DIV", "ADD_S", "MUL_S", "DIV_S", "RSUB_S", "RDIV_S", "POW_I", "SQRT",
+    "LOG_EPS", "EXP", "RELU", "TANH", "GELU", "NEG", "COPY_Y", "MASK_FILL", "CAUSAL_FILL", "CLAMP", "FMA_S",
+    "DIV_BWD_B", "POW_BWD", "SQRT_BWD", "LOG_BWD", "RDIV_BWD", "RELU_BWD", "TANH_BWD", "GELU_BWD", "MASK_BWD",
+    "CAUSAL_BWD", "VAR_BWD", "STD_BWD", "XENT_PROB_BWD", "MSE_BWD", "SCALE_SHIFT",
+]
+EW = {name: i for i, name in enumerate(_EW_NAMES)}
+
+RED_SUM, RED_MEAN, RED_VAR, RED_STD = range(4)
+EPI_NONE, EPI_GELU, EPI_DGELU, EPI_RELU, EPI_DRELU = range(5)
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("D", C.c_void_p),
+        ("bias", C.c_void_p), ("aux", C.c_void_p), ("residual", C.c_void_p),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("batch", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldd", C.c_int64),
+        ("a_bs", C.c_int64), ("b_bs", C.c_int64), ("d_bs", C.c_int64), ("bias_bs", C.c_int64),
+        ("a_kmajor", C.c_int), ("b_kmajor", C.c_int), ("out_dtype", C.c_int), ("bias_dtype", C.c_int),
+        ("epi", C.c_int), ("alpha", C.c_float), ("status", C.c_void_p),
+    ]
+
+
+class AttnFwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64), ("dk", C.c_int64),
+        ("q_row", C.c_int64), ("k_row", C.c_int64), ("v_row", C.c_int64), ("o_row", C.c_int64),
+        ("q_bs", C.c_int64), ("k_bs", C.c_int64), ("v_bs", C.c_int64), ("o_bs", C.c_int64),
+        ("scale", C.c_float), ("causal", C.c_int), ("status", C.c_void_p),
+    ]
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("d_o", C.c_void_p),
+        ("lse", C.c_void_p), ("dq", C.c_void_p), ("dk_", C.c_void_p), ("dv", C.c_void_p), ("delta", C.c_void_p),
+        ("dq_acc", C.c_void_p),
+        ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64), ("dk", C.c_int64),
+        ("row", C.c_int64), ("bs", C.c_int64),
+        ("scale", C.c_float), ("causal", C.c_int), ("status", C.c_void_p),
+    ]
+
+
+_i64, _i32, _f32, _vp, _u64 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_uint64
+
+_SIGS = {
+    "dg_elementwise": [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _f32, _i64, _i64, _i64, _vp],
+    "dg_cast": [_i32, _vp, _i32, _vp, _i64, _vp],
+    "dg_accumulate": [_i32, _vp, _vp, _i64, _vp],
+    "dg_strided_copy": [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp],
+    "dg_transpose2d": [_i32, _vp, _vp, _i64, _i64, _i64, _vp],
+    "dg_reduce_rows": [_i32, _vp, _vp, _vp, _i64, _i64, _i32, _vp],
+    "dg_reduce_cols": [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp],
+    "dg_sum_all": [_i32, _vp, _vp, _i64, _f32, _vp, _vp],
+    "dg_softmax_fwd": [_i32, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _i64, _vp],
+    "dg_softmax_bwd": [_i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _i64, _vp],
+    "dg_layernorm_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp],
+    "dg_layernorm_bwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp],
+    "dg_embedding_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
+    "dg_embedding_bwd": [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
+    "dg_index_from_float": [_vp, _vp, _i64, _i64, _vp, _vp],
+    "dg_one_hot": [_vp, _vp, _i64, _i64, _vp],
+    "dg_xent_fwd_bwd": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp],
+    "dg_adam_step": [_i32, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _i32, _f32, _vp],
+    "dg_sgd_step": [_i32, _vp, _vp, _i32, _vp, _i64, _f32, _f32, _vp],
+    "dg_adam_multi": [_i32, _i32, _vp, _vp, _i64, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _vp],
+    "dg_randn": [_i32, _vp, _i64, _u64, _u64, _f32, _f32, _vp],
+    "dg_fill": [_i32, _vp, _i64, _f32, _vp],
+    "dg_gemm_simt": [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                     _f32, _f32, _vp],
+    "dg_gemm_sm100": [C.POINTER(GemmArgs), _vp],
+    "dg_gemm_sm100_supported": [C.POINTER(GemmArgs)],
+    "dg_attention_fwd_sm100": [C.POINTER(AttnFwdArgs), _vp],
+    "dg_attention_bwd_sm100": [C.POINTER(AttnBwdArgs), _vp],
+    "dg_version": [],
+    "dg_device_sm_count": [],
+}
+_RET64 = {"dg_reduce_cols_scratch_bytes": [_i64, _i64, _i64], "dg_layernorm_bwd_scratch_bytes": [_i64, _i64]}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def load(build_if_missing: bool = True):
+    """Load (building first if needed) the kernel library. Raises on failure."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not LIB_PATH.exists():
+            if not build_if_missing:
+                raise KernelLibraryError(f"{LIB_PATH} is missing; run python -m dummygrad_b200._build")
+            from . import _build
+            _build.build_kernels()
+        try:
+            lib = C.CDLL(str(LIB_PATH))
+        except OSError as e:  # pragma: no cover - depends on the host
+            raise KernelLibraryError(f"cannot load {LIB_PATH}: {e}") from e
+        for name, sig in _SIGS.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                continue
+            fn.argtypes = sig
+            fn.restype = C.c_int
+        for name, sig in _RET64.items():
+            fn = getattr(lib, name)
+            fn.argtypes = sig
+            fn.restype = C.c_int64
+        _LIB = lib
+    return _LIB
+
+
+def has(name: str) -> bool:
+    return hasattr(load(), name)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise TypeError(f"unsupported dtype {dt}; the kernel library handles float32 and bfloat16")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        if rc > 0:
+            raise KernelLibraryError(f"{what}: CUDA error {rc} ({_cuda_err_name(rc)})")
+        names = {-1: "bad argument", -2: "unsupported shape/alignment", -3: "driver/tensor-map failure",
+                 -4: "size too large"}
+        raise KernelLibraryError(f"{what}: {names.get(rc, rc)}")
+
+
+def _cuda_err_name(rc: int) -> str:
+    try:
+        from cuda.bindings import runtime as rt  # type: ignore
+        return str(rt.cudaGetErrorName(rt.cudaError_t(rc))[1])
+    except Exception:
+        return "see cudaError_t"
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()

@@ -1,0 +1,1217 @@
+"""The differentiable op set.
+
+The first part mirrors the reference's 40 free functions and their backward nodes
+(src/ops.h, src/scalar_ops.h, src/broadcasting.h, src/matmul.h, src/transpose.h, src/view.h,
+src/concat.h, src/cool_ops.h, src/masking.h, src/softmax.h, src/sum.h, src/mean.h, src/var.h,
+src/std.h, src/loss.h, src/activations.h) with the same names, argument conventions and
+numerical definitions (log's +1e-8, biased variance, -1e9 mask fill, losses normalised by the
+total element count, ``axis == 0`` meaning the second-to-last dim for
+mean/var/std_dev/broadcast/concat). Unlike the reference every op is correct for strided
+inputs and gradients are never aliased.
+
+The second part adds fused nodes that the modules use on the hot path: ``linear`` (GEMM with
+bias / activation / residual epilogue), ``layer_norm``, ``embedding``, ``attention`` and
+``softmax_cross_entropy``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+import torch
+
+from .. import _lib as L
+from .._lib import BC_COL, BC_COLS, BC_MAT, BC_ROW, BC_ROWS, BC_SAME, BC_SCALAR, RED_MEAN, RED_STD, RED_SUM, RED_VAR
+from ..tensor import ONE, Node, Tensor, get_grad_edge, materialize
+from . import kernels as K
+
+LOG_EPS = 1e-8
+STD_EPS = 1e-8
+
+
+# ----------------------------------------------------------------------------- plumbing
+def _result(data: torch.Tensor, node_factory, inputs: Sequence[Tensor]) -> Tensor:
+    out = Tensor._wrap(data, False)
+    if any(t.requires_grad for t in inputs):
+        node = node_factory()
+        for t in inputs:
+            node.add_next_edge(get_grad_edge(t).function, 0)
+        out.requires_grad = True
+        out.grad_fn = node
+    return out
+
+
+def _c(t: Tensor) -> torch.Tensor:
+    """Contiguous device buffer of a tensor (gather copy for views)."""
+    return K.contiguous(t.data)
+
+
+def _grad(grads, shape, dtype, device) -> torch.Tensor:
+    """Incoming gradient as a contiguous tensor of the expected shape."""
+    g = materialize(grads[0], shape, dtype, device)
+    g = K.contiguous(g)
+    if tuple(g.shape) != tuple(shape):
+        g = g.reshape(shape)
+    if g.dtype != dtype:
+        g = K.cast(g, dtype)
+    return g
+
+
+def _same_shape(a: Tensor, b: Tensor, what: str) -> None:
+    if a.shape != b.shape:
+        raise RuntimeError(f"{what}: shapes {a.shape} and {b.shape} differ")
+
+
+def _rc(shape) -> tuple[int, int, int]:
+    c = shape[-1]
+    r = shape[-2] if len(shape) >= 2 else 1
+    return math.prod(shape) // (r * c) if r * c else 0, r, c
+
+
+# ----------------------------------------------------------------------------- binary ops (src/ops.h)
+class AddBackward(Node):
+    def __init__(self, shape, dtype, device):
+        super().__init__()
+        self.meta = (shape, dtype, device)
+
+    def apply(self, grads):
+        g = grads[0]
+        return [g, g]  # the engine never accumulates into a gradient it does not own
+
+
+def add(a: Tensor, b: Tensor) -> Tensor:
+    _same_shape(a, b, "add")
+    return _result(K.ew("ADD", _c(a), _c(b)), lambda: AddBackward(a.shape, a.dtype, a.device), (a, b))
+
+
+class SubBackward(Node):
+    def __init__(self, shape, dtype, device):
+        super().__init__()
+        self.meta = (shape, dtype, device)
+
+    def apply(self, grads):
+        g = _grad(grads, *self.meta)
+        return [g, K.ew("NEG", g)]
+
+
+def sub(a: Tensor, b: Tensor) -> Tensor:
+    _same_shape(a, b, "sub")
+    return _result(K.ew("SUB", _c(a), _c(b)), lambda: SubBackward(a.shape, a.dtype, a.device), (a, b))
+
+
+class MulBackward(Node):
+    def __init__(self, a, b):
+        super().__init__()
+        self.a, self.b = a, b
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("MUL", g, self.b), K.ew("MUL", g, self.a)]
+
+    def release_variables(self):
+        self.a = self.b = None
+
+
+def mul(a: Tensor, b: Tensor) -> Tensor:
+    _same_shape(a, b, "mul")
+    ad, bd = _c(a), _c(b)
+    return _result(K.ew("MUL", ad, bd), lambda: MulBackward(ad, bd), (a, b))
+
+
+class DivBackward(Node):
+    def __init__(self, a, b):
+        super().__init__()
+        self.a, self.b = a, b
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("DIV", g, self.b), K.ew("DIV_BWD_B", g, self.b, self.a)]
+
+    def release_variables(self):
+        self.a = self.b = None
+
+
+def div(a: Tensor, b: Tensor) -> Tensor:
+    _same_shape(a, b, "div")
+    ad, bd = _c(a), _c(b)
+    return _result(K.ew("DIV", ad, bd), lambda: DivBackward(ad, bd), (a, b))
+
+
+class PowBackward(Node):
+    def __init__(self, a, n):
+        super().__init__()
+        self.a, self.n = a, n
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("POW_BWD", g, self.a, s0=float(self.n))]
+
+    def release_variables(self):
+        self.a = None
+
+
+def pow(a: Tensor, n: int) -> Tensor:  # noqa: A001 - reference name
+    if int(n) != n:
+        raise RuntimeError("pow: integer exponents only")
+    ad = _c(a)
+    return _result(K.ew("POW_I", ad, s0=float(int(n))), lambda: PowBackward(ad, int(n)), (a,))
+
+
+class SqrtBackward(Node):
+    def __init__(self, a):
+        super().__init__()
+        self.a = a
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("SQRT_BWD", g, self.a)]
+
+
+def sqrt(a: Tensor) -> Tensor:
+    ad = _c(a)
+    return _result(K.ew("SQRT", ad), lambda: SqrtBackward(ad), (a,))
+
+
+class LogBackward(Node):
+    def __init__(self, a, eps):
+        super().__init__()
+        self.a, self.eps = a, eps
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("LOG_BWD", g, self.a, s0=self.eps)]
+
+
+def log(a: Tensor) -> Tensor:
+    """log(a + 1e-8), the reference's definition (src/ops.h:295-297)."""
+    ad = _c(a)
+    return _result(K.ew("LOG_EPS", ad, s0=LOG_EPS), lambda: LogBackward(ad, LOG_EPS), (a,))
+
+
+class ExpBackward(Node):
+    def __init__(self, out):
+        super().__init__()
+        self.out = out
+
+    def apply(self, grads):
+        g = _grad(grads, self.out.shape, self.out.dtype, self.out.device)
+        return [K.ew("MUL", g, self.out)]
+
+
+def exp(a: Tensor) -> Tensor:
+    od = K.ew("EXP", _c(a))
+    return _result(od, lambda: ExpBackward(od), (a,))
+
+
+class SimpleSumBackward(Node):
+    def __init__(self, shape, dtype, device):
+        super().__init__()
+        self.meta = (shape, dtype, device)
+
+    def apply(self, grads):
+        shape, dtype, device = self.meta
+        if grads[0] is ONE:
+            return [K.fill_(torch.empty(shape, dtype=dtype, device=device), 1.0)]
+        g = K.contiguous(grads[0]).reshape(1)
+        return [K.ew("COPY_Y", None, g if g.dtype == dtype else K.cast(g, dtype), ymode=BC_SCALAR, shape=shape)]
+
+
+def simple_sum(a: Tensor) -> Tensor:
+    """Sum of all elements -> shape [1, 1] (src/ops.h:350-385)."""
+    od = K.sum_all(_c(a)).reshape(1, 1)
+    return _result(od, lambda: SimpleSumBackward(tuple(a.shape), a.dtype, a.device), (a,))
+
+
+# ----------------------------------------------------------------------------- scalar ops (src/scalar_ops.h)
+class _ScaleBackward(Node):
+    """g * factor (factor 1 passes the gradient through)."""
+
+    def __init__(self, factor, shape, dtype, device):
+        super().__init__()
+        self.factor, self.meta = factor, (shape, dtype, device)
+
+    def apply(self, grads):
+        if self.factor == 1.0:
+            return [grads[0]]
+        return [K.ew("MUL_S", _grad(grads, *self.meta), s0=self.factor)]
+
+
+class AddScalarBackward(_ScaleBackward):
+    pass
+
+
+class SubScalarBackward(_ScaleBackward):
+    pass
+
+
+class MulScalarBackward(_ScaleBackward):
+    pass
+
+
+class DivScalarBackward(_ScaleBackward):
+    pass
+
+
+class RsubScalarBackward(_ScaleBackward):
+    pass
+
+
+def add_scalar(a: Tensor, s: float) -> Tensor:
+    return _result(K.ew("ADD_S", _c(a), s0=s), lambda: AddScalarBackward(1.0, a.shape, a.dtype, a.device), (a,))
+
+
+def sub_scalar(a: Tensor, s: float) -> Tensor:
+    return _result(K.ew("ADD_S", _c(a), s0=-s), lambda: SubScalarBackward(1.0, a.shape, a.dtype, a.device), (a,))
+
+
+def mul_scalar(a: Tensor, s: float) -> Tensor:
+    return _result(K.ew("MUL_S", _c(a), s0=s), lambda: MulScalarBackward(float(s), a.shape, a.dtype, a.device), (a,))
+
+
+def div_scalar(a: Tensor, s: float) -> Tensor:
+    return _result(K.ew("DIV_S", _c(a), s0=s), lambda: DivScalarBackward(1.0 / s, a.shape, a.dtype, a.device), (a,))
+
+
+def neg(a: Tensor) -> Tensor:
+    return mul_scalar(a, -1.0)
+
+
+def rsub_scalar(s: float, a: Tensor) -> Tensor:
+    return _result(K.ew("RSUB_S", _c(a), s0=s), lambda: RsubScalarBackward(-1.0, a.shape, a.dtype, a.device), (a,))
+
+
+class RdivScalarBackward(Node):
+    def __init__(self, a, s):
+        super().__init__()
+        self.a, self.s = a, s
+
+    def apply(self, grads):
+        g = _grad(grads, self.a.shape, self.a.dtype, self.a.device)
+        return [K.ew("RDIV_BWD", g, self.a, s0=self.s)]
+
+
+def rdiv_scalar(s: float, a: Tensor) -> Tensor:
+    ad = _c(a)
+    return _result(K.ew("RDIV_S", ad, s0=s), lambda: RdivScalarBackward(ad, float(s)), (a,))
+
+
+# ----------------------------------------------------------------------------- broadcasting (src/broadcasting.h)
+class BroadcastBackward(Node):
+    def __init__(self, in_shape, out_shape, axis0, dtype, device):
+        super().__init__()
+        self.in_shape, self.out_shape, self.axis0, self.dtype, self.device = in_shape, out_shape, axis0, dtype, device
+
+    def apply(self, grads):
+        g = _grad(grads, self.out_shape, self.dtype, self.device)
+        B, r, c = _rc(self.out_shape)
+        if self.axis0:
+            out, _ = K.reduce_cols(g.reshape(B, r, c), RED_SUM)
+        else:
+            out, _ = K.reduce_rows(g.reshape(B * r, c), RED_SUM)
+        return [out.reshape(self.in_shape)]
+
+
+def broadcast(a: Tensor, axis: int, n: int) -> Tensor:
+    """Repeat the size-1 second-to-last dim (axis 0) or last dim (otherwise) n times."""
+    if a.ndim() < 2:
+        raise RuntimeError("broadcast: needs at least 2 dims")
+    shape = a.shape
+    dim = -2 if axis == 0 else -1
+    if shape[dim] != 1:
+        raise RuntimeError("broadcast: the broadcast dim must have size 1")
+    out_shape = list(shape)
+    out_shape[dim] = int(n)
+    od = K.ew("COPY_Y", None, _c(a), ymode=BC_COLS if axis == 0 else BC_ROWS, shape=out_shape)
+    return _result(od, lambda: BroadcastBackward(shape, out_shape, axis == 0, a.dtype, a.device), (a,))
+
+
+def _cast_mode(x: Tensor, y: Tensor, what: str) -> int:
+    if x.ndim() < 2:
+        raise RuntimeError(f"{what}: x must have at least 2 dims")
+    if y.ndim() == x.ndim() and y.ndim() > 2 and y.shape[:-2] == x.shape[:-2] and math.prod(x.shape[:-2]) > 1:
+        # keepdim statistic of x itself ([.., r, 1] or [.., 1, c]): broadcast per batch entry.
+        # (The reference indexes such a y with batch 0's values for every batch entry,
+        # src/broadcasting.h:133-149; the per-entry reading is the intended one.)
+        if y.shape[-1] == 1 and y.shape[-2] == x.shape[-2]:
+            return BC_ROWS
+        if y.shape[-2] == 1 and y.shape[-1] == x.shape[-1]:
+            return BC_COLS
+        if y.shape[-2:] == x.shape[-2:]:
+            return BC_SAME
+        raise RuntimeError(f"{what}: y shape {y.shape} does not broadcast against {x.shape}")
+    if y.ndim() > 2 and math.prod(y.shape[:-2]) == 1:
+        pass
+    elif y.ndim() != 2:
+        raise RuntimeError(f"{what}: y must be 2-D (or a keepdim statistic of x)")
+    r, c = x.shape[-2], x.shape[-1]
+    yr, yc = y.shape[-2], y.shape[-1]
+    if yr not in (1, r) or yc not in (1, c):
+        raise RuntimeError(f"{what}: y shape {y.shape} does not broadcast against {x.shape}")
+    if yr == r and yc == c:
+        return BC_MAT
+    if yr == 1 and yc == c:
+        return BC_ROW
+    if yr == r and yc == 1:
+        return BC_COL
+    return BC_SCALAR
+
+
+def _reduce_to_y(full: torch.Tensor, mode: int, yshape) -> torch.Tensor:
+    """Sum a [batch, r, c] gradient over batch and over y's size-1 dims."""
+    B, r, c = _rc(full.shape)
+    if mode == BC_ROW:
+        out, _ = K.reduce_cols(full.reshape(1, B * r, c), RED_SUM)
+    elif mode == BC_COL:
+        rows, _ = K.reduce_rows(full.reshape(B * r, c), RED_SUM)
+        out, _ = K.reduce_cols(rows.reshape(1, B, r), RED_SUM)
+    elif mode == BC_MAT:
+        out, _ = K.reduce_cols(full.reshape(1, B, r * c), RED_SUM)
+    elif mode == BC_ROWS:
+        out, _ = K.reduce_rows(full.reshape(B * r, c), RED_SUM)
+    elif mode == BC_COLS:
+        out, _ = K.reduce_cols(full.reshape(B, r, c), RED_SUM)
+    elif mode == BC_SAME:
+        out = full
+    else:
+        out = K.sum_all(full)
+    return out.reshape(list(yshape))
+
+
+class _CastBackward(Node):
+    kind = ""
+
+    def __init__(self, x, y, mode, xshape, yshape, dtype, device):
+        super().__init__()
+        self.x, self.y, self.mode = x, y, mode
+        self.xshape, self.yshape, self.dtype, self.device = xshape, yshape, dtype, device
+
+    def apply(self, grads):
+        g = _grad(grads, self.xshape, self.dtype, self.device)
+        m = self.mode
+        if self.kind == "add":
+            return [g, _reduce_to_y(g, m, self.yshape)]
+        if self.kind == "sub":
+            return [g, _reduce_to_y(K.ew("NEG", g), m, self.yshape)]
+        if self.kind == "mul":
+            return [K.ew("MUL", g, self.y, ymode=m), _reduce_to_y(K.ew("MUL", g, self.x), m, self.yshape)]
+        gx = K.ew("DIV", g, self.y, ymode=m)
+        gy_full = K.ew("DIV_BWD_B", g, self.y, self.x, ymode=m)
+        return [gx, _reduce_to_y(gy_full, m, self.yshape)]
+
+    def release_variables(self):
+        self.x = self.y = None
+
+
+class CastAddBackward(_CastBackward):
+    kind = "add"
+
+
+class CastSubBackward(_CastBackward):
+    kind = "sub"
+
+
+class CastMulBackward(_CastBackward):
+    kind = "mul"
+
+
+class CastDivBackward(_CastBackward):
+    kind = "div"
+
+
+def _cast_n(op: str, cls, x: Tensor, y: Tensor, save: bool) -> Tensor:
+    mode = _cast_mode(x, y, f"cast_n_{op.lower()}")
+    xd, yd = _c(x), _c(y)
+    if yd.dtype != xd.dtype:
+        yd = K.cast(yd, xd.dtype)
+    od = K.ew(op, xd, yd, ymode=mode)
+    return _result(od, lambda: cls(xd if save else None, yd if save else None, mode, tuple(x.shape), tuple(y.shape),
+                                   x.dtype, x.device), (x, y))
+
+
+def cast_n_add(x: Tensor, y: Tensor) -> Tensor:
+    return _cast_n("ADD", CastAddBackward, x, y, False)
+
+
+def cast_n_sub(x: Tensor, y: Tensor) -> Tensor:
+    return _cast_n("SUB", CastSubBackward, x, y, False)
+
+
+def cast_n_mul(x: Tensor, y: Tensor) -> Tensor:
+    return _cast_n("MUL", CastMulBackward, x, y, True)
+
+
+def cast_n_div(x: Tensor, y: Tensor) -> Tensor:
+    return _cast_n("DIV", CastDivBackward, x, y, True)
+
+
+# ----------------------------------------------------------------------------- matmul (src/matmul.h)
+def _broadcast_batch(sa, sb):
+    la, lb = list(sa), list(sb)
+    n = max(len(la), len(lb))
+    la = [1] * (n - len(la)) + la
+    lb = [1] * (n - len(lb)) + lb
+    out = []
+    for x, y in zip(la, lb):
+        if x != y and x != 1 and y != 1:
+            raise RuntimeError(f"matmul: batch dims {sa} and {sb} are not broadcast-compatible")
+        out.append(max(x, y))
+    return out, la, lb
+
+
+def _expand_operand(t: torch.Tensor, padded_batch, out_batch) -> torch.Tensor:
+    """Return an operand whose batch dims are either absent (pure broadcast) or equal to out_batch."""
+    if all(d == 1 for d in padded_batch):
+        return t.reshape(t.shape[-2], t.shape[-1])
+    if list(padded_batch) == list(out_batch):
+        return t.reshape(*out_batch, t.shape[-2], t.shape[-1])
+    v = t.reshape(*padded_batch, t.shape[-2], t.shape[-1]).expand(*out_batch, t.shape[-2], t.shape[-1])
+    return K.contiguous(v)
+
+
+def _sum_to_batch(full: torch.Tensor, padded_batch, out_batch, orig_shape) -> torch.Tensor:
+    """Sum a gradient with batch dims ``out_batch`` down to an operand whose padded batch dims are given."""
+    if list(padded_batch) == list(out_batch):
+        return full.reshape(orig_shape)
+    r, c = full.shape[-2], full.shape[-1]
+    nb = len(out_batch)
+    red = [i for i in range(nb) if padded_batch[i] == 1 and out_batch[i] != 1]
+    keep = [i for i in range(nb) if i not in red]
+    perm = red + keep + [nb, nb + 1]
+    moved = K.contiguous(full.reshape(*out_batch, r, c).permute(perm))
+    R = math.prod(out_batch[i] for i in red)
+    rest = math.prod(out_batch[i] for i in keep) * r * c
+    out, _ = K.reduce_cols(moved.reshape(1, R, rest), RED_SUM)
+    return out.reshape(orig_shape)
+
+
+class MatmulBackward(Node):
+    """dA = G B^T and dB = A^T G, summed over broadcast batch dims (src/matmul.h:39-79).
+    ``tb`` marks a B operand that arrived as a transposed view of a contiguous [.., N, K]
+    buffer: it is consumed in place through the K-major descriptor and its gradient is produced
+    directly in that buffer's layout."""
+
+    def __init__(self, a, b, pa, pb, out_batch, ashape, bshape, tb):
+        super().__init__()
+        self.a, self.b, self.pa, self.pb, self.out_batch = a, b, pa, pb, out_batch
+        self.ashape, self.bshape, self.tb = ashape, bshape, tb
+
+    def apply(self, grads):
+        a, b, tb = self.a, self.b, self.tb
+        M, Kd = a.shape[-2], a.shape[-1]
+        N = b.shape[-2] if tb else b.shape[-1]
+        g = _grad(grads, (*self.out_batch, M, N), a.dtype, a.device)
+        a2, b2 = a.dim() == 2, b.dim() == 2
+        # dA = G B^T
+        if b2:
+            dA = K.gemm2d(g.reshape(-1, N), b, trans_b=not tb).reshape(*self.out_batch, M, Kd)
+        else:
+            dA = K.gemm2d(g, b, trans_b=not tb)
+        dA = _sum_to_batch(dA, self.pa, self.out_batch, self.ashape)
+        # dB = A^T G   (or dB^T = G^T A when B is held transposed)
+        if b2 and not a2:
+            af, gf = a.reshape(-1, Kd), g.reshape(-1, N)
+            dB = K.gemm2d(gf, af, trans_a=True) if tb else K.gemm2d(af, gf, trans_a=True)
+            dB = dB.transpose(-1, -2) if tb else dB
+        else:
+            full = K.gemm2d(g, a, trans_a=True) if tb else K.gemm2d(a, g, trans_a=True)
+            if tb:
+                tshape = tuple(self.bshape[:-2]) + (self.bshape[-1], self.bshape[-2])
+                dB = _sum_to_batch(full, self.pb, self.out_batch, tshape).transpose(-1, -2)
+            else:
+                dB = _sum_to_batch(full, self.pb, self.out_batch, self.bshape)
+        return [dA, dB]
+
+    def release_variables(self):
+        self.a = self.b = None
+
+
+def manual_matmul(a: Tensor, b: Tensor) -> Tensor:
+    """Batched [.., r1, c1] x [.., c1, c2] with NumPy broadcasting of the leading dims."""
+    if a.ndim() < 2 or b.ndim() < 2:
+        raise RuntimeError("matmul: both operands need at least 2 dims")
+    if a.shape[-1] != b.shape[-2]:
+        raise RuntimeError(f"matmul: inner dims {a.shape[-1]} and {b.shape[-2]} differ")
+    out_batch, pa, pb = _broadcast_batch(a.shape[:-2], b.shape[:-2])
+    M, N = a.shape[-2], b.shape[-1]
+    tb = (not b.data.is_contiguous()) and b.data.transpose(-1, -2).is_contiguous() and b.dtype == a.dtype
+    bd0 = b.data.transpose(-1, -2) if tb else _c(b)
+    if bd0.dtype != a.dtype:
+        bd0 = K.cast(bd0, a.dtype)
+    ad = _expand_operand(_c(a), pa, out_batch)
+    bd = _expand_operand(bd0, pb, out_batch)
+    if bd.dim() == 2 and ad.dim() > 2:
+        od = K.gemm2d(ad.reshape(-1, ad.shape[-1]), bd, trans_b=tb).reshape(*out_batch, M, N)
+    else:
+        od = K.gemm2d(ad, bd, trans_b=tb).reshape(*out_batch, M, N)
+    return _result(od, lambda: MatmulBackward(ad, bd, pa, pb, out_batch, tuple(a.shape), tuple(b.shape), tb), (a, b))
+
+
+def matmul(a: Tensor, b: Tensor) -> Tensor:
+    return manual_matmul(a, b)
+
+
+# ----------------------------------------------------------------------------- views (src/transpose.h, src/view.h)
+class TransposeBackward(Node):
+    def __init__(self, d0, d1):
+        super().__init__()
+        self.d0, self.d1 = d0, d1
+
+    def apply(self, grads):
+        g = grads[0]
+        if g is ONE:
+            return [g]
+        return [g.transpose(self.d0, self.d1)]  # a view; consumers normalise the layout
+
+
+def transpose(a: Tensor, d0: int = -2, d1: int = -1) -> Tensor:
+    if a.ndim() < 2:
+        raise RuntimeError("transpose: needs at least 2 dims")
+    return _result(a.data.transpose(d0, d1), lambda: TransposeBackward(d0, d1), (a,))
+
+
+class ViewBackward(Node):
+    def __init__(self, in_shape):
+        super().__init__()
+        self.in_shape = in_shape
+
+    def apply(self, grads):
+        g = grads[0]
+        if g is ONE:
+            return [g]
+        return [K.contiguous(g).reshape(self.in_shape)]
+
+
+def view(a: Tensor, shape: Sequence[int]) -> Tensor:
+    if not a.is_contiguous():
+        raise RuntimeError("view: tensor is not contiguous")
+    shape = [int(s) for s in shape]
+    if math.prod(shape) != a.size():
+        raise RuntimeError("view: element count differs")
+    return _result(a.data.view(shape), lambda: ViewBackward(tuple(a.shape)), (a,))
+
+
+def reshape(a: Tensor, shape: Sequence[int]) -> Tensor:
+    shape = [int(s) for s in shape]
+    if math.prod(shape) != a.size():
+        raise RuntimeError("reshape: element count differs")
+    return _result(_c(a).view(shape), lambda: ViewBackward(tuple(a.shape)), (a,))
+
+
+# ----------------------------------------------------------------------------- concat (src/concat.h)
+class ConcatBackward(Node):
+    def __init__(self, dim, na, nb, out_shape, dtype, device):
+        super().__init__()
+        self.dim, self.na, self.nb, self.out_shape, self.dtype, self.device = dim, na, nb, out_shape, dtype, device
+
+    def apply(self, grads):
+        g = _grad(grads, self.out_shape, self.dtype, self.device)
+        ga = K.contiguous(g.narrow(self.dim, 0, self.na))
+        gb = K.contiguous(g.narrow(self.dim, self.na, self.nb))
+        return [ga, gb]
+
+
+def concat(a: Tensor, b: Tensor, axis: int) -> Tensor:
+    """Join along the second-to-last dim (axis 0) or the last dim (otherwise)."""
+    if a.ndim() < 2 or a.ndim() != b.ndim():
+        raise RuntimeError("concat: operands need the same rank >= 2")
+    dim = a.ndim() - 2 if axis == 0 else a.ndim() - 1
+    for i, (x, y) in enumerate(zip(a.shape, b.shape)):
+        if i != dim and x != y:
+            raise RuntimeError(f"concat: shapes {a.shape} and {b.shape} differ outside the joined dim")
+    out_shape = list(a.shape)
+    out_shape[dim] = a.shape[dim] + b.shape[dim]
+    od = torch.empty(out_shape, dtype=a.dtype, device=a.device)
+    K.strided_copy(od.narrow(dim, 0, a.shape[dim]), a.data)
+    K.strided_copy(od.narrow(dim, a.shape[dim], b.shape[dim]), b.data if b.dtype == a.dtype else K.cast(b.data, a.dtype))
+    return _result(od, lambda: ConcatBackward(dim, a.shape[dim], b.shape[dim], tuple(out_shape), a.dtype, a.device),
+                   (a, b))
+
+
+# ----------------------------------------------------------------------------- scale_n_shift (src/cool_ops.h)
+class ScaleAndShiftBackward(Node):
+    def __init__(self, x, gamma):
+        super().__init__()
+        self.x, self.gamma = x, gamma
+
+    def apply(self, grads):
+        x = self.x
+        g = _grad(grads, x.shape, x.dtype, x.device)
+        B, r, c = _rc(x.shape)
+        gx = K.ew("MUL", g, self.gamma, ymode=BC_ROW)
+        gg, _ = K.reduce_cols(K.ew("MUL", g, x).reshape(1, B * r, c), RED_SUM)
+        gb, _ = K.reduce_cols(g.reshape(1, B * r, c), RED_SUM)
+        return [gx, gg.reshape(1, c), gb.reshape(1, c)]
+
+    def release_variables(self):
+        self.x = self.gamma = None
+
+
+def scale_n_shift(x: Tensor, gamma: Tensor, beta: Tensor) -> Tensor:
+    """Per-feature affine x * gamma[j] + beta[j] with gamma, beta of shape [1, c]."""
+    c = x.shape[-1]
+    if gamma.size() != c or beta.size() != c:
+        raise RuntimeError("scale_n_shift: gamma/beta must have one entry per feature")
+    xd, gd, bd = _c(x), _c(gamma).reshape(c), _c(beta).reshape(c)
+    od = K.ew("SCALE_SHIFT", xd, gd, bd, ymode=BC_ROW, zmode=BC_ROW)
+    return _result(od, lambda: ScaleAndShiftBackward(xd, gd), (x, gamma, beta))
+
+
+# ----------------------------------------------------------------------------- masks, softmax
+class BoolMaskBackward(Node):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+
+    def apply(self, grads):
+        g = _grad(grads, self.m.shape, self.m.dtype, self.m.device)
+        return [K.ew("MASK_BWD", g, self.m)]
+
+
+def bool_mask(a: Tensor, m: Tensor) -> Tensor:
+    """m == 0 ? -1e9 : a, with m of a's full shape (src/masking.h:5-63)."""
+    _same_shape(a, m, "bool_mask")
+    md = _c(m)
+    if md.dtype != a.dtype:
+        md = K.cast(md, a.dtype)
+    return _result(K.ew("MASK_FILL", _c(a), md, s0=K.MASK_FILL_VALUE), lambda: BoolMaskBackward(md), (a,))
+
+
+class CausalMaskBackward(Node):
+    def __init__(self, shape, dtype, device):
+        super().__init__()
+        self.meta = (shape, dtype, device)
+
+    def apply(self, grads):
+        return [K.ew("CAUSAL_BWD", _grad(grads, *self.meta))]
+
+
+def causal_mask(a: Tensor) -> Tensor:
+    """col > row ? -1e9 : a on the last two dims (src/masking.h:66-120)."""
+    if a.ndim() < 2:
+        raise RuntimeError("causal_mask: needs at least 2 dims")
+    return _result(K.ew("CAUSAL_FILL", _c(a), s0=K.MASK_FILL_VALUE),
+                   lambda: CausalMaskBackward(tuple(a.shape), a.dtype, a.device), (a,))
+
+
+class SoftmaxBackward(Node):
+    def __init__(self, out, mask=None, mask_mode=0, scale=1.0):
+        super().__init__()
+        self.out, self.mask, self.mask_mode, self.scale = out, mask, mask_mode, scale
+
+    def apply(self, grads):
+        g = _grad(grads, self.out.shape, self.out.dtype, self.out.device)
+        return [K.softmax_bwd(g, self.out, self.mask, self.mask_mode, self.scale)]
+
+
+def softmax(a: Tensor) -> Tensor:
+    od = K.softmax_fwd(_c(a), None, 0, 1.0)
+    return _result(od, lambda: SoftmaxBackward(od), (a,))
+
+
+def masked_softmax(a: Tensor, scale: float = 1.0, causal: bool = False, mask: Tensor | None = None) -> Tensor:
+    """softmax(mask(scale * a)) in one kernel; same mathematics as mul_scalar -> mask -> softmax."""
+    md = None
+    mode = 1 if causal else 0
+    if mask is not None:
+        md = _c(mask)
+        if md.dtype != a.dtype:
+            md = K.cast(md, a.dtype)
+        mode = 2
+    od = K.softmax_fwd(_c(a), md, mode, scale)
+    return _result(od, lambda: SoftmaxBackward(od, md, mode, scale), (a,))
+
+
+# ----------------------------------------------------------------------------- reductions
+def _axis_is_rows(ndim: int, axis: int, legacy: bool) -> bool:
+    """True when the reduction runs over the second-to-last dim."""
+    if legacy:
+        return axis == 0
+    ax = axis + ndim if axis < 0 else axis
+    if ax == ndim - 1:
+        return False
+    if ax == ndim - 2:
+        return True
+    raise RuntimeError("sum: only the last two dims can be reduced")
+
+
+def _reduce(a: Tensor, over_rows: bool, mode: int, want_mean=False):
+    ad = _c(a)
+    shape = a.shape
+    if a.ndim() < 2:
+        raise RuntimeError("reduction needs at least 2 dims")
+    B, r, c = _rc(shape)
+    if over_rows:
+        out, mean = K.reduce_cols(ad.reshape(B, r, c), mode, want_mean)
+        oshape = list(shape[:-2]) + [1, c]
+    else:
+        out, mean = K.reduce_rows(ad.reshape(B * r, c), mode, want_mean)
+        oshape = list(shape[:-1]) + [1]
+    return ad, out.reshape(oshape), mean
+
+
+class SumBackward(Node):
+    def __init__(self, shape, over_rows, scale, dtype, device):
+        super().__init__()
+        self.shape, self.over_rows, self.scale, self.dtype, self.device = shape, over_rows, scale, dtype, device
+
+    def apply(self, grads):
+        oshape = list(self.shape)
+        oshape[-2 if self.over_rows else -1] = 1
+        g = _grad(grads, oshape, self.dtype, self.device)
+        out = K.ew("COPY_Y", None, g, ymode=BC_COLS if self.over_rows else BC_ROWS, shape=self.shape)
+        if self.scale != 1.0:
+            out = K.ew("MUL_S", out, s0=self.scale, out=out)
+        return [out]
+
+
+class MeanBackward(SumBackward):
+    pass
+
+
+def sum(a: Tensor, axis: int) -> Tensor:  # noqa: A001 - reference name
+    """Keepdim sum over one of the last two dims; ``axis`` is a real (possibly negative) index."""
+    over_rows = _axis_is_rows(a.ndim(), axis, legacy=False)
+    _, od, _ = _reduce(a, over_rows, RED_SUM)
+    return _result(od, lambda: SumBackward(tuple(a.shape), over_rows, 1.0, a.dtype, a.device), (a,))
+
+
+def mean(a: Tensor, axis: int) -> Tensor:
+    """Keepdim mean; axis 0 = second-to-last dim, anything else = last dim (src/mean.h:64)."""
+    over_rows = _axis_is_rows(a.ndim(), axis, legacy=True)
+    n = a.shape[-2] if over_rows else a.shape[-1]
+    _, od, _ = _reduce(a, over_rows, RED_MEAN)
+    return _result(od, lambda: MeanBackward(tuple(a.shape), over_rows, 1.0 / n, a.dtype, a.device), (a,))
+
+
+class VarBackward(Node):
+    def __init__(self, a, mean, over_rows, n):
+        super().__init__()
+        self.a, self.mean, self.over_rows, self.n = a, mean, over_rows, n
+
+    def apply(self, grads):
+        a = self.a
+        oshape = list(a.shape)
+        oshape[-2 if self.over_rows else -1] = 1
+        g = _grad(grads, oshape, a.dtype, a.device)
+        mode = BC_COLS if self.over_rows else BC_ROWS
+        return [K.ew("VAR_BWD", a, self.mean, g, ymode=mode, zmode=mode, s0=2.0 / self.n)]
+
+    def release_variables(self):
+        self.a = self.mean = None
+
+
+def var(a: Tensor, axis: int) -> Tensor:
+    """Biased (divide by N) keepdim variance (src/var.h:82,98)."""
+    over_rows = _axis_is_rows(a.ndim(), axis, legacy=True)
+    n = a.shape[-2] if over_rows else a.shape[-1]
+    ad, od, mu = _reduce(a, over_rows, RED_VAR, want_mean=True)
+    return _result(od, lambda: VarBackward(ad, mu, over_rows, n), (a,))
+
+
+class StdDevBackward(Node):
+    def __init__(self, a, mean, std, over_rows, n):
+        super().__init__()
+        self.a, self.mean, self.std, self.over_rows, self.n = a, mean, std, over_rows, n
+
+    def apply(self, grads):
+        a = self.a
+        oshape = list(a.shape)
+        oshape[-2 if self.over_rows else -1] = 1
+        g = _grad(grads, oshape, a.dtype, a.device)
+        mode = BC_COLS if self.over_rows else BC_ROWS
+        return [K.ew("STD_BWD", a, self.mean, g, self.std, ymode=mode, zmode=mode, wmode=mode, s0=1.0 / self.n,
+                     s1=STD_EPS)]
+
+
+def std_dev(a: Tensor, axis: int) -> Tensor:
+    """sqrt of the biased variance; gradient (a - mu) / (N (sigma + 1e-8)) (src/std.h:32-35)."""
+    over_rows = _axis_is_rows(a.ndim(), axis, legacy=True)
+    n = a.shape[-2] if over_rows else a.shape[-1]
+    ad, od, mu = _reduce(a, over_rows, RED_STD, want_mean=True)
+    sd = od.reshape(-1)
+    return _result(od, lambda: StdDevBackward(ad, mu, sd, over_rows, n), (a,))
+
+
+# ----------------------------------------------------------------------------- losses (src/loss.h)
+def _gscalar(grads, dtype, device) -> torch.Tensor:
+    g = grads[0]
+    if g is ONE:
+        return K.fill_(torch.empty(1, dtype=dtype, device=device), 1.0)
+    g = K.contiguous(g).reshape(1)
+    return g if g.dtype == dtype else K.cast(g, dtype)
+
+
+class CrossEntropyBackward(Node):
+    def __init__(self, pred, target, n):
+        super().__init__()
+        self.pred, self.target, self.n = pred, target, n
+
+    def apply(self, grads):
+        p = self.pred
+        g = _gscalar(grads, p.dtype, p.device)
+        return [K.ew("XENT_PROB_BWD", p, self.target, g, zmode=BC_SCALAR, s0=1.0 / self.n), None]
+
+
+def cross_entropy(pred: Tensor, target: Tensor) -> Tensor:
+    """-sum(t * log(p + 1e-8)) / n on probabilities, n = rows * classes (src/loss.h:27-52)."""
+    _same_shape(pred, target, "cross_entropy")
+    pd, td = _c(pred), _c(target)
+    if td.dtype != pd.dtype:
+        td = K.cast(td, pd.dtype)
+    n = pred.size()
+    lp = K.ew("LOG_EPS", pd, s0=LOG_EPS)
+    od = K.sum_all(K.ew("MUL", lp, td, out=lp), scale=-1.0 / n).reshape(1, 1)
+    return _result(od, lambda: CrossEntropyBackward(pd, td, n), (pred, target))
+
+
+class MseBackward(Node):
+    def __init__(self, pred, target, n):
+        super().__init__()
+        self.pred, self.target, self.n = pred, target, n
+
+    def apply(self, grads):
+        p = self.pred
+        g = _gscalar(grads, p.dtype, p.device)
+        gp = K.ew("MSE_BWD", p, self.target, g, zmode=BC_SCALAR, s0=2.0 / self.n)
+        return [gp, K.ew("NEG", gp)]
+
+
+def mse(pred: Tensor, target: Tensor) -> Tensor:
+    """sum((p - t)^2) / n -> [1, 1] (src/loss.h:55-103)."""
+    _same_shape(pred, target, "mse")
+    pd, td = _c(pred), _c(target)
+    if td.dtype != pd.dtype:
+        td = K.cast(td, pd.dtype)
+    n = pred.size()
+    d = K.ew("SUB", pd, td)
+    od = K.sum_all(K.ew("MUL", d, d, out=d), scale=1.0 / n).reshape(1, 1)
+    return _result(od, lambda: MseBackward(pd, td, n), (pred, target))
+
+
+# ----------------------------------------------------------------------------- activations (src/activations.h)
+class _ActBackward(Node):
+    op = ""
+
+    def __init__(self, saved):
+        super().__init__()
+        self.saved = saved
+
+    def apply(self, grads):
+        s = self.saved
+        return [K.ew(self.op, _grad(grads, s.shape, s.dtype, s.device), s)]
+
+
+class ReluBackward(_ActBackward):
+    op = "RELU_BWD"
+
+
+class TanhBackward(_ActBackward):
+    op = "TANH_BWD"
+
+
+class GeluBackward(_ActBackward):
+    op = "GELU_BWD"
+
+
+def relu(a: Tensor) -> Tensor:
+    ad = _c(a)
+    return _result(K.ew("RELU", ad), lambda: ReluBackward(ad), (a,))
+
+
+def tanh(a: Tensor) -> Tensor:
+    od = K.ew("TANH", _c(a))
+    return _result(od, lambda: TanhBackward(od), (a,))
+
+
+def gelu(a: Tensor) -> Tensor:
+    """tanh approximation with the reference's constants (src/activations.h:118-119)."""
+    ad = _c(a)
+    return _result(K.ew("GELU", ad), lambda: GeluBackward(ad), (a,))
+
+
+# ----------------------------------------------------------------------------- user-level extension example
+class SliceLastBackward(Node):
+    """x[:, -1, :] backward: scatter into the last position (the reference defines this node in a
+    program, src/mars.cpp:14-58, which is what makes ``Node`` a public extension point)."""
+
+    def __init__(self, shape, dtype, device):
+        super().__init__()
+        self.shape, self.dtype, self.device = shape, dtype, device
+
+    def apply(self, grads):
+        B, S, D = self.shape
+        g = _grad(grads, (B, D), self.dtype, self.device)
+        out = K.fill_(torch.empty(self.shape, dtype=self.dtype, device=self.device), 0.0)
+        K.strided_copy(out[:, S - 1, :], g)
+        return [out]
+
+
+def slice_last(x: Tensor) -> Tensor:
+    if x.ndim() != 3:
+        raise RuntimeError("slice_last: expects [B, S, D]")
+    od = K.contiguous(x.data[:, -1, :])
+    return _result(od, lambda: SliceLastBackward(tuple(x.shape), x.dtype, x.device), (x,))
+
+
+def clamp_(t: torch.Tensor, lo: float, hi: float) -> torch.Tensor:
+    """In-place value clipping of a raw buffer (gradient clamp of src/mars.cpp:242-249)."""
+    c = K.contiguous(t)
+    K.ew("CLAMP", c, s0=lo, s1=hi, out=c)
+    if c is not t:
+        K.strided_copy(t, c)
+    return t
+
+
+# ============================================================================= fused nodes
+class LinearBackward(Node):
+    """Backward of y = act(x W + b) (+ residual): dgrad and wgrad GEMMs with operand layouts taken
+    through descriptors (no transposes), activation derivative fused in the dgrad-side epilogue."""
+
+    def __init__(self, x2d, W, pre_act, act, has_bias, xshape, has_res, W_tensor):
+        super().__init__()
+        self.x2d, self.W, self.pre_act, self.act = x2d, W, pre_act, act
+        self.has_bias, self.xshape, self.has_res = has_bias, xshape, has_res
+        self.W_tensor = W_tensor
+
+    def apply(self, grads):
+        W, x2d = self.W, self.x2d
+        Kin, N = W.shape
+        g = _grad(grads, (*self.xshape[:-1], N), x2d.dtype, x2d.device).reshape(-1, N)
+        gres = g if self.has_res else None
+        if self.act is not None:
+            g = K.ew("GELU_BWD" if self.act == "gelu" else "RELU_BWD", g, self.pre_act)
+        dx = K.gemm2d(g, W, trans_b=True).reshape(self.xshape)
+        dW = K.gemm2d(x2d, g, trans_a=True)
+        outs = [dx, dW]
+        if self.has_bias:
+            db, _ = K.reduce_cols(g.reshape(1, g.shape[0], N), RED_SUM)
+            outs.append(db.reshape(1, N))
+        if self.has_res:
+            outs.append(gres.reshape(*self.xshape[:-1], N))
+        return outs
+
+    def release_variables(self):
+        self.x2d = self.W = self.pre_act = None
+
+
+def linear(x: Tensor, W: Tensor, b: Tensor | None = None, act: str | None = None,
+           residual: Tensor | None = None) -> Tensor:
+    """act(x @ W + b) + residual with W stored [in, out] (src/linear.h:26) as ONE GEMM launch:
+    bias, GELU/ReLU and the residual add run in the GEMM epilogue."""
+    Kin, N = W.shape
+    if x.shape[-1] != Kin:
+        raise RuntimeError(f"linear: input features {x.shape[-1]} != {Kin}")
+    xd = _c(x).reshape(-1, Kin)
+    Wd = _c(W)
+    bd = _c(b).reshape(N) if b is not None else None
+    rd = _c(residual).reshape(-1, N) if residual is not None else None
+    epi = {None: L.EPI_NONE, "gelu": L.EPI_GELU, "relu": L.EPI_RELU}[act]
+    pre = None
+    if act is not None and (x.requires_grad or W.requires_grad):
+        pre = torch.empty(xd.shape[0], N, dtype=torch.bfloat16 if xd.dtype == torch.bfloat16 else xd.dtype,
+                          device=xd.device)
+    od = K.gemm2d(xd, Wd, bias=bd, epi=epi, aux=pre, residual=rd).reshape(*x.shape[:-1], N)
+    inputs = [x, W] + ([b] if b is not None else []) + ([residual] if residual is not None else [])
+    return _result(od, lambda: LinearBackward(xd, Wd, pre, act, b is not None, tuple(x.shape), residual is not None, W),
+                   inputs)
+
+
+class LayerNormBackward(Node):
+    def __init__(self, x, gamma, mean, rstd):
+        super().__init__()
+        self.x, self.gamma, self.mean, self.rstd = x, gamma, mean, rstd
+
+    def apply(self, grads):
+        x = self.x
+        g = _grad(grads, x.shape, x.dtype, x.device)
+        dx, dg, db = K.layernorm_bwd(g, x, self.gamma, self.mean, self.rstd)
+        d = x.shape[-1]
+        return [dx, dg.reshape(1, d), db.reshape(1, d)]
+
+    def release_variables(self):
+        self.x = self.gamma = self.mean = self.rstd = None
+
+
+def layer_norm(x: Tensor, gamma: Tensor, beta: Tensor, eps: float = 1e-5) -> Tensor:
+    """One-kernel LayerNorm over the last dim (biased variance, eps inside the sqrt); the fused
+    equivalent of the reference's seven-op chain (src/layernorm.h:29-39)."""
+    d = x.shape[-1]
+    xd = _c(x)
+    gd, bd = _c(gamma).reshape(d), _c(beta).reshape(d)
+    y, mu, rstd = K.layernorm_fwd(xd, gd, bd, eps)
+    return _result(y, lambda: LayerNormBackward(xd, gd, mu, rstd), (x, gamma, beta))
+
+
+class EmbeddingBackward(Node):
+    def __init__(self, idx, pos_idx, vocab, npos, dtype):
+        super().__init__()
+        self.idx, self.pos_idx, self.vocab, self.npos, self.dtype = idx, pos_idx, vocab, npos, dtype
+
+    def apply(self, grads):
+        g = K.contiguous(grads[0])
+        g = g.reshape(-1, g.shape[-1])
+        outs = [K.embedding_bwd(g, self.idx, self.vocab)]
+        if self.pos_idx is not None:
+            outs.append(K.embedding_bwd(g, self.pos_idx, self.npos))
+        return outs
+
+
+def embedding(table: Tensor, idx, pos_table: Tensor | None = None, pos_idx=None) -> Tensor:
+    """Row gather ``table[idx]`` (+ ``pos_table[pos_idx]`` in the same kernel) -> [n, d].
+    Indices may be float tensors (reference convention, src/embedding.h:19-22) or int64."""
+    V, d = table.shape
+    it = idx.data if isinstance(idx, Tensor) else idx
+    ii = K.index_from_float(it, V)
+    pi = None
+    if pos_table is not None:
+        pt = pos_idx.data if isinstance(pos_idx, Tensor) else pos_idx
+        pi = K.index_from_float(pt, pos_table.shape[0])
+    od = K.embedding_fwd(_c(table), ii, _c(pos_table) if pos_table is not None else None, pi)
+    inputs = [table] + ([pos_table] if pos_table is not None else [])
+    return _result(od, lambda: EmbeddingBackward(ii, pi, V, pos_table.shape[0] if pos_table is not None else 0,
+                                                 table.dtype), inputs)
+
+
+def one_hot(idx, classes: int) -> Tensor:
+    """Float indices -> [n, classes] one-hot rows, no grad (src/init.h:53-65)."""
+    it = idx.data if isinstance(idx, Tensor) else idx
+    ii = K.index_from_float(it, classes)
+    return Tensor._wrap(K.one_hot(ii, classes), False)
+
+
+class SoftmaxCrossEntropyBackward(Node):
+    def __init__(self, dlogits, shape):
+        super().__init__()
+        self.dlogits, self.shape = dlogits, shape
+
+    def apply(self, grads):
+        g = grads[0]
+        d = self.dlogits
+        if g is not ONE:
+            gs = K.contiguous(g).reshape(1)
+            d = K.ew("MUL", d, gs if gs.dtype == d.dtype else K.cast(gs, d.dtype), ymode=BC_SCALAR, out=d)
+        return [d.reshape(self.shape)]
+
+    def release_variables(self):
+        self.dlogits = None
+
+
+def softmax_cross_entropy(logits: Tensor, targets, reduction: str = "mean", inplace_grad: bool = False) -> Tensor:
+    """Fused logits -> loss with integer targets. ``reduction``: "mean" divides by the number of
+    rows (standard), "reference" by rows * classes (src/loss.h:32,43). dlogits is produced by
+    the same kernel, so the backward is free unless the incoming gradient is not 1."""
+    V = logits.shape[-1]
+    ld = _c(logits).reshape(-1, V)
+    T = ld.shape[0]
+    tt = targets.data if isinstance(targets, Tensor) else targets
+    ti = K.index_from_float(tt, V)
+    denom = T if reduction == "mean" else T * V
+    loss_rows, dlogits = K.xent_fwd_bwd(ld, ti, 1.0 / denom, inplace=inplace_grad)
+    od = K.sum_all(loss_rows, scale=1.0 / denom).reshape(1, 1)  # fp32 whatever the logits dtype
+    return _result(od, lambda: SoftmaxCrossEntropyBackward(dlogits, tuple(logits.shape)), (logits,))
+
+
+class AttentionBackward(Node):
+    """Composite attention backward on batched GEMMs + the fused mask-softmax backward."""
+
+    def __init__(self, q, k, v, p, scale, causal):
+        super().__init__()
+        self.q, self.k, self.v, self.p, self.scale, self.causal = q, k, v, p, scale, causal
+
+    def apply(self, grads):
+        q, k, v, p = self.q, self.k, self.v, self.p
+        g = _grad(grads, q.shape[:-1] + (v.shape[-1],), q.dtype, q.device)
+        dv = K.gemm2d(p, g, trans_a=True)
+        dp = K.gemm2d(g, v, trans_b=True)
+        ds = K.softmax_bwd(dp, p, None, 1 if self.causal else 0, self.scale)
+        dq = K.gemm2d(ds, k)
+        dk = K.gemm2d(ds, q, trans_a=True)
+        return [dq, dk, dv]
+
+    def release_variables(self):
+        self.q = self.k = self.v = self.p = None
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = False, scale: float | None = None) -> Tensor:
+    """softmax(mask(q k^T * scale)) v for [B, H, S, dk] operands (src/attention.h:84-90)."""
+    dk = q.shape[-1]
+    scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    qd, kd, vd = _c(q), _c(k), _c(v)
+    s = K.gemm2d(qd, kd, trans_b=True)
+    p = K.softmax_fwd(s, None, 1 if causal else 0, scale)
+    od = K.gemm2d(p, vd)
+    return _result(od, lambda: AttentionBackward(qd, kd, vd, p, scale, causal), (q, k, v))
+
+
+class MhaCoreBackward(Node):
+    def __init__(self, inner, B, S, H, dk):
+        super().__init__()
+        self.inner, self.dims = inner, (B, S, H, dk)
+
+    def apply(self, grads):
+        B, S, H, dk = self.dims
+        q = self.inner.q
+        g = _grad(grads, (B, S, H * dk), q.dtype, q.device)
+        gh = K.contiguous(g.reshape(B, S, H, dk).transpose(1, 2))
+        dq, dkk, dv = self.inner.apply([gh])
+        back = lambda t: K.contiguous(t.transpose(1, 2)).reshape(B, S, H * dk)  # noqa: E731
+        return [back(dq), back(dkk), back(dv)]
+
+    def release_variables(self):
+        self.inner.release_variables()
+
+
+def mha_core(q: Tensor, k: Tensor, v: Tensor, n_heads: int, causal: bool = False, scale: float | None = None) -> Tensor:
+    """Multi-head attention between the projections: q, k, v [B, S, H*dk] -> merged [B, S, H*dk]
+    (the split / transpose / attention / merge steps of src/attention.h:79-93 as one node)."""
+    B, S, D = q.shape
+    H = n_heads
+    dk = D // H
+    scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    split = lambda t: K.contiguous(_c(t).reshape(B, S, H, dk).transpose(1, 2))  # noqa: E731
+    qd, kd, vd = split(q), split(k), split(v)
+    s = K.gemm2d(qd, kd, trans_b=True)
+    p = K.softmax_fwd(s, None, 1 if causal else 0, scale)
+    od = K.contiguous(K.gemm2d(p, vd).transpose(1, 2)).reshape(B, S, D)
+    return _result(od, lambda: MhaCoreBackward(AttentionBackward(qd, kd, vd, p, scale, causal), B, S, H, dk), (q, k, v))
+
+
+class MlpBackward(Node):
+    """Backward of fc2(gelu(fc1(x))) (+ residual). The GELU derivative runs in the epilogue of the
+    GEMM that produces dH, so the [tokens, d_ff] gradient is written once."""
+
+    def __init__(self, x2d, W1, W2, pre, h, xshape, has_res):
+        super().__init__()
+        self.x2d, self.W1, self.W2, self.pre, self.h, self.xshape, self.has_res = x2d, W1, W2, pre, h, xshape, has_res
+
+    def apply(self, grads):
+        x2d, W1, W2 = self.x2d, self.W1, self.W2
+        d_ff, d_out = W2.shape
+        g = _grad(grads, (*self.xshape[:-1], d_out), x2d.dtype, x2d.device).reshape(-1, d_out)
+        dW2 = K.gemm2d(self.h, g, trans_a=True)
+        db2, _ = K.reduce_cols(g.reshape(1, g.shape[0], d_out), RED_SUM)
+        dh = K.gemm2d(g, W2, trans_b=True, epi=L.EPI_DGELU, aux=self.pre)
+        dW1 = K.gemm2d(x2d, dh, trans_a=True)
+        db1, _ = K.reduce_cols(dh.reshape(1, dh.shape[0], d_ff), RED_SUM)
+        dx = K.gemm2d(dh, W1, trans_b=True).reshape(self.xshape)
+        outs = [dx, dW1, db1.reshape(1, d_ff), dW2, db2.reshape(1, d_out)]
+        if self.has_res:
+            outs.append(g.reshape(*self.xshape[:-1], d_out))
+        return outs
+
+    def release_variables(self):
+        self.x2d = self.W1 = self.W2 = self.pre = self.h = None
+
+
+def mlp(x: Tensor, W1: Tensor, b1: Tensor, W2: Tensor, b2: Tensor, residual: Tensor | None = None) -> Tensor:
+    """fc2(gelu(fc1(x))) + residual as two GEMM launches (src/transformer.h:20-23)."""
+    d_in, d_ff = W1.shape
+    d_out = W2.shape[1]
+    xd = _c(x).reshape(-1, d_in)
+    W1d, W2d = _c(W1), _c(W2)
+    pre = torch.empty(xd.shape[0], d_ff, dtype=xd.dtype, device=xd.device)
+    h = K.gemm2d(xd, W1d, bias=_c(b1).reshape(d_ff), epi=L.EPI_GELU, aux=pre)
+    rd = _c(residual).reshape(-1, d_out) if residual is not None else None
+    od = K.gemm2d(h, W2d, bias=_c(b2).reshape(d_out), residual=rd).reshape(*x.shape[:-1], d_out)
+    inputs = [x, W1, b1, W2, b2] + ([residual] if residual is not None else [])
+    return _result(od, lambda: MlpBackward(xd, W1d, W2d, pre, h, tuple(x.shape), residual is not None), inputs)

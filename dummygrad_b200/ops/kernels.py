@@ -1,0 +1,619 @@
+"""Kernel-level functions on raw ``torch.Tensor`` buffers.
+
+Each function has two implementations selected by the tensor's device:
+
+* CUDA tensors go to the hand-written sm_100a kernels in ``libdgb200.so`` (never to PyTorch
+  math; a missing library raises).
+* CPU tensors use a plain PyTorch statement of the same mathematics. That path exists so
+  the engine, the modules and the distributed host logic can be exercised without a GPU
+  (``gloo`` ranks), and it is what GPU numerics tests compare against.
+
+The autograd layer (:mod:`dummygrad_b200.tensor`, :mod:`dummygrad_b200.ops`) is built on
+these functions only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _lib as L
+from .._lib import (BC_COL, BC_COLS, BC_MAT, BC_ROW, BC_ROWS, BC_SAME, BC_SCALAR, EW, RED_MEAN, RED_STD, RED_SUM,
+                    RED_VAR)
+
+MASK_FILL_VALUE = -1e9
+_GELU_K, _GELU_A = 0.7978845608, 0.044715
+
+# counts launches of this library's kernels (bench.py reports it)
+launch_count = 0
+
+
+def _cnt(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _is_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# ----------------------------------------------------------------------------- helpers
+def _bc_view(t: torch.Tensor, mode: int, n: int, r: int, c: int) -> torch.Tensor:
+    """CPU path: view a broadcast operand so it broadcasts against a [batch, r, c] tensor."""
+    if mode == BC_SAME:
+        return t.reshape(-1, r, c)
+    if mode == BC_ROW:
+        return t.reshape(1, 1, c)
+    if mode == BC_COL:
+        return t.reshape(1, r, 1)
+    if mode == BC_SCALAR:
+        return t.reshape(1, 1, 1)
+    if mode == BC_MAT:
+        return t.reshape(1, r, c)
+    if mode == BC_ROWS:
+        return t.reshape(-1, r, 1)
+    if mode == BC_COLS:
+        return t.reshape(-1, 1, c)
+    raise ValueError(mode)
+
+
+def _gelu_cpu(x):
+    return 0.5 * x * (1.0 + torch.tanh(_GELU_K * (x + _GELU_A * x ** 3)))
+
+
+def _gelu_grad_cpu(x):
+    u = _GELU_K * (x + _GELU_A * x ** 3)
+    t = torch.tanh(u)
+    du = _GELU_K * (1.0 + 3.0 * _GELU_A * x * x)
+    return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * du
+
+
+def _ew_cpu(op, x, y, z, w, s0, s1, r, c):
+    name = L._EW_NAMES[op]
+    f = {
+        "COPY": lambda: x, "ADD": lambda: x + y, "SUB": lambda: x - y, "MUL": lambda: x * y, "DIV": lambda: x / y,
+        "ADD_S": lambda: x + s0, "MUL_S": lambda: x * s0, "DIV_S": lambda: x / s0, "RSUB_S": lambda: s0 - x,
+        "RDIV_S": lambda: s0 / x, "POW_I": lambda: x ** int(s0), "SQRT": lambda: torch.sqrt(x),
+        "LOG_EPS": lambda: torch.log(x + s0), "EXP": lambda: torch.exp(x), "RELU": lambda: torch.clamp_min(x, 0),
+        "TANH": lambda: torch.tanh(x), "GELU": lambda: _gelu_cpu(x), "NEG": lambda: -x,
+        "COPY_Y": lambda: y,
+        "MASK_FILL": lambda: torch.where(y == 0, torch.full_like(x, s0), x),
+        "CLAMP": lambda: torch.clamp(x, s0, s1), "FMA_S": lambda: x * s0 + y * s1,
+        "DIV_BWD_B": lambda: -x * z / (y * y), "POW_BWD": lambda: s0 * y ** (int(s0) - 1) * x,
+        "SQRT_BWD": lambda: 0.5 * x / torch.sqrt(y), "LOG_BWD": lambda: x / (y + s0),
+        "RDIV_BWD": lambda: -s0 * x / (y * y), "RELU_BWD": lambda: torch.where(y > 0, x, torch.zeros_like(x)),
+        "TANH_BWD": lambda: (1 - y * y) * x, "GELU_BWD": lambda: _gelu_grad_cpu(y) * x,
+        "MASK_BWD": lambda: torch.where(y != 0, x, torch.zeros_like(x)),
+        "VAR_BWD": lambda: s0 * (x - y) * z, "MSE_BWD": lambda: s0 * (x - y) * z,
+        "STD_BWD": lambda: s0 * (x - y) * z / (w + s1), "XENT_PROB_BWD": lambda: -(y / x) * s0 * z,
+        "SCALE_SHIFT": lambda: x * y + z,
+    }
+    if name in ("CAUSAL_FILL", "CAUSAL_BWD"):
+        i = torch.arange(r).reshape(1, r, 1)
+        j = torch.arange(c).reshape(1, 1, c)
+        fut = j > i
+        return torch.where(fut, torch.full_like(x, s0 if name == "CAUSAL_FILL" else 0.0), x)
+    return f[name]()
+
+
+def ew(op: str | int, x: torch.Tensor | None, y=None, z=None, w=None, *, ymode=BC_SAME, zmode=BC_SAME,
+       wmode=BC_SAME, s0: float = 0.0, s1: float = 0.0, shape=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Pointwise op over a contiguous tensor viewed as [batch, r, c] (r, c = last two dims)."""
+    if isinstance(op, str):
+        op = EW[op]
+    ref = x if x is not None else y
+    shape = tuple(shape if shape is not None else ref.shape)
+    n = math.prod(shape)
+    c = shape[-1] if len(shape) >= 1 else 1
+    r = shape[-2] if len(shape) >= 2 else 1
+    if out is None:
+        out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
+    if n == 0:
+        return out
+    if _is_cuda(ref):
+        lib = L.load()
+        for t in (x, y, z, w):
+            assert t is None or t.is_contiguous(), "kernel operands must be contiguous"
+        L.check(lib.dg_elementwise(op, L.dtype_code(ref.dtype), out.data_ptr(), L.ptr(x), L.ptr(y), L.ptr(z),
+                                   L.ptr(w), ymode, zmode, wmode, float(s0), float(s1), n, r, c, L.stream_ptr()),
+                f"dg_elementwise[{L._EW_NAMES[op]}]")
+        _cnt()
+        return out
+    xv = None if x is None else x.reshape(-1, r, c).float()
+    yv = None if y is None else _bc_view(y, ymode, n, r, c).float()
+    zv = None if z is None else _bc_view(z, zmode, n, r, c).float()
+    wv = None if w is None else _bc_view(w, wmode, n, r, c).float()
+    res = _ew_cpu(op, xv, yv, zv, wv, s0, s1, r, c)
+    out.copy_(res.expand(n // (r * c), r, c).reshape(shape).to(out.dtype))
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    if not _is_cuda(x):
+        return x.to(dtype)
+    x = contiguous(x)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    L.check(L.load().dg_cast(L.dtype_code(dtype), out.data_ptr(), L.dtype_code(x.dtype), x.data_ptr(), x.numel(),
+                             L.stream_ptr()), "dg_cast")
+    _cnt()
+    return out
+
+
+def assign_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """dst[...] = src (contiguous, same shape), converting dtype if they differ."""
+    if not _is_cuda(dst):
+        dst.copy_(src)
+        return dst
+    assert dst.is_contiguous() and src.is_contiguous() and dst.numel() == src.numel()
+    L.check(L.load().dg_cast(L.dtype_code(dst.dtype), dst.data_ptr(), L.dtype_code(src.dtype), src.data_ptr(),
+                             src.numel(), L.stream_ptr()), "dg_cast")
+    _cnt()
+    return dst
+
+
+def accumulate_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """dst += src in place (both contiguous, same dtype)."""
+    if not _is_cuda(dst):
+        dst.add_(src.to(dst.dtype))
+        return dst
+    assert dst.is_contiguous() and src.is_contiguous() and dst.dtype == src.dtype
+    L.check(L.load().dg_accumulate(L.dtype_code(dst.dtype), dst.data_ptr(), src.data_ptr(), dst.numel(),
+                                   L.stream_ptr()), "dg_accumulate")
+    _cnt()
+    return dst
+
+
+def _i64arr(vals):
+    return (C.c_int64 * len(vals))(*vals)
+
+
+def strided_copy(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """dst[...] = src[...] for two same-shape views of any strides."""
+    assert dst.shape == src.shape and dst.dtype == src.dtype
+    if dst.numel() == 0:
+        return dst
+    if not _is_cuda(dst):
+        dst.copy_(src)
+        return dst
+    shape = list(src.shape) or [1]
+    ds = list(dst.stride()) or [1]
+    ss = list(src.stride()) or [1]
+    if len(shape) > 8:
+        raise ValueError("strided_copy supports at most 8 dims")
+    L.check(L.load().dg_strided_copy(L.dtype_code(src.dtype), dst.data_ptr(), _i64arr(ds), src.data_ptr(),
+                                     _i64arr(ss), _i64arr(shape), len(shape), L.stream_ptr()), "dg_strided_copy")
+    _cnt()
+    return dst
+
+
+def contiguous(x: torch.Tensor) -> torch.Tensor:
+    """Stride-aware gather into a fresh contiguous buffer (identity when already contiguous)."""
+    if x.is_contiguous():
+        return x
+    if not _is_cuda(x):
+        return x.contiguous()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    # batched 2-D transpose fast path
+    if x.dim() >= 2 and x.transpose(-1, -2).is_contiguous():
+        R, Cc = x.shape[-1], x.shape[-2]  # source is [.., R, Cc] contiguous
+        B = x.numel() // (R * Cc)
+        if B <= 65535:
+            L.check(L.load().dg_transpose2d(L.dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), B, R, Cc,
+                                            L.stream_ptr()), "dg_transpose2d")
+            _cnt()
+            return out
+    return strided_copy(out, x)
+
+
+# ----------------------------------------------------------------------------- reductions
+def reduce_rows(x: torch.Tensor, mode: int, want_mean: bool = False):
+    """x [R, C] contiguous -> [R] (fp32 accumulate). Returns (out, mean or None)."""
+    R, Cc = x.shape
+    if not _is_cuda(x):
+        xf = x.float()
+        mu = xf.mean(dim=1)
+        res = {RED_SUM: lambda: xf.sum(1), RED_MEAN: lambda: mu, RED_VAR: lambda: xf.var(1, unbiased=False),
+               RED_STD: lambda: xf.var(1, unbiased=False).sqrt()}[mode]()
+        return res.to(x.dtype), (mu.to(x.dtype) if want_mean else None)
+    out = torch.empty(R, dtype=x.dtype, device=x.device)
+    mean = torch.empty(R, dtype=x.dtype, device=x.device) if want_mean else None
+    L.check(L.load().dg_reduce_rows(L.dtype_code(x.dtype), out.data_ptr(), L.ptr(mean), x.data_ptr(), R, Cc, mode,
+                                    L.stream_ptr()), "dg_reduce_rows")
+    _cnt()
+    return out, mean
+
+
+def reduce_cols(x: torch.Tensor, mode: int, want_mean: bool = False):
+    """x [B, R, C] contiguous -> [B, C]. Returns (out, mean or None)."""
+    B, R, Cc = x.shape
+    if not _is_cuda(x):
+        xf = x.float()
+        mu = xf.mean(dim=1)
+        res = {RED_SUM: lambda: xf.sum(1), RED_MEAN: lambda: mu, RED_VAR: lambda: xf.var(1, unbiased=False),
+               RED_STD: lambda: xf.var(1, unbiased=False).sqrt()}[mode]()
+        return res.to(x.dtype), (mu.to(x.dtype) if want_mean else None)
+    lib = L.load()
+    out = torch.empty(B, Cc, dtype=x.dtype, device=x.device)
+    mean = torch.empty(B, Cc, dtype=x.dtype, device=x.device) if (want_mean or mode >= RED_VAR) else None
+    scratch = torch.empty(max(int(lib.dg_reduce_cols_scratch_bytes(B, R, Cc)), 4), dtype=torch.uint8, device=x.device)
+    L.check(lib.dg_reduce_cols(L.dtype_code(x.dtype), out.data_ptr(), L.ptr(mean), x.data_ptr(), B, R, Cc, mode,
+                               scratch.data_ptr(), L.stream_ptr()), "dg_reduce_cols")
+    _cnt(2 if mode <= RED_MEAN else 4)
+    return out, (mean if want_mean else None)
+
+
+def sum_all(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Sum of every element times ``scale`` -> tensor of shape [1] (same dtype)."""
+    if not _is_cuda(x):
+        return (x.float().sum() * scale).reshape(1).to(x.dtype)
+    x = contiguous(x)
+    out = torch.empty(1, dtype=x.dtype, device=x.device)
+    scratch = torch.empty(1024, dtype=torch.float32, device=x.device)
+    L.check(L.load().dg_sum_all(L.dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), x.numel(), float(scale),
+                                scratch.data_ptr(), L.stream_ptr()), "dg_sum_all")
+    _cnt(2)
+    return out
+
+
+# ----------------------------------------------------------------------------- softmax / mask
+def softmax_fwd(x: torch.Tensor, mask: torch.Tensor | None, mask_mode: int, scale: float) -> torch.Tensor:
+    """softmax over the last dim of (scale*x) with masked entries replaced by -1e9.
+    mask_mode: 0 none, 1 causal on the last two dims, 2 tensor mask (0 = masked)."""
+    c = x.shape[-1]
+    r = x.shape[-2] if x.dim() >= 2 else 1
+    rows = x.numel() // max(c, 1)
+    if not _is_cuda(x):
+        v = x.float() * scale
+        if mask_mode == 1:
+            i = torch.arange(r).reshape(r, 1)
+            j = torch.arange(c).reshape(1, c)
+            v = torch.where(j > i, torch.full_like(v, MASK_FILL_VALUE), v)
+        elif mask_mode == 2:
+            v = torch.where(mask == 0, torch.full_like(v, MASK_FILL_VALUE), v)
+        return torch.softmax(v, dim=-1).to(x.dtype)
+    out = torch.empty_like(x)
+    L.check(L.load().dg_softmax_fwd(L.dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), L.ptr(mask), mask_mode,
+                                    float(scale), rows, r, c, L.stream_ptr()), "dg_softmax_fwd")
+    _cnt()
+    return out
+
+
+def softmax_bwd(g: torch.Tensor, s: torch.Tensor, mask: torch.Tensor | None, mask_mode: int, scale: float):
+    c = s.shape[-1]
+    r = s.shape[-2] if s.dim() >= 2 else 1
+    rows = s.numel() // max(c, 1)
+    if not _is_cuda(s):
+        gf, sf = g.float(), s.float()
+        gx = scale * sf * (gf - (gf * sf).sum(-1, keepdim=True))
+        if mask_mode == 1:
+            i = torch.arange(r).reshape(r, 1)
+            j = torch.arange(c).reshape(1, c)
+            gx = torch.where(j > i, torch.zeros_like(gx), gx)
+        elif mask_mode == 2:
+            gx = torch.where(mask == 0, torch.zeros_like(gx), gx)
+        return gx.to(s.dtype)
+    out = torch.empty_like(s)
+    L.check(L.load().dg_softmax_bwd(L.dtype_code(s.dtype), out.data_ptr(), g.data_ptr(), s.data_ptr(), L.ptr(mask),
+                                    mask_mode, float(scale), rows, r, c, L.stream_ptr()), "dg_softmax_bwd")
+    _cnt()
+    return out
+
+
+# ----------------------------------------------------------------------------- layernorm
+def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float):
+    """x [..., d] contiguous. Returns (y, mean[rows] fp32, rstd[rows] fp32)."""
+    d = x.shape[-1]
+    rows = x.numel() // d
+    if not _is_cuda(x):
+        xf = x.float().reshape(rows, d)
+        mu = xf.mean(1)
+        var = xf.var(1, unbiased=False)
+        rstd = torch.rsqrt(var + eps)
+        y = (xf - mu[:, None]) * rstd[:, None] * gamma.float().reshape(1, d) + beta.float().reshape(1, d)
+        return y.reshape(x.shape).to(x.dtype), mu, rstd
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    L.check(L.load().dg_layernorm_fwd(L.dtype_code(x.dtype), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                      x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), rows, d, float(eps),
+                                      L.stream_ptr()), "dg_layernorm_fwd")
+    _cnt()
+    return y, mean, rstd
+
+
+def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True):
+    """Returns (dx or None, dgamma [d] or None, dbeta [d] or None)."""
+    d = x.shape[-1]
+    rows = x.numel() // d
+    if not _is_cuda(x):
+        gf = g.float().reshape(rows, d)
+        xf = x.float().reshape(rows, d)
+        xh = (xf - mean[:, None]) * rstd[:, None]
+        gh = gf * gamma.float().reshape(1, d)
+        dx = rstd[:, None] * (gh - gh.mean(1, keepdim=True) - xh * (gh * xh).mean(1, keepdim=True))
+        dg = (gf * xh).sum(0)
+        db = gf.sum(0)
+        return (dx.reshape(x.shape).to(x.dtype) if need_dx else None,
+                dg.to(x.dtype) if need_dparams else None, db.to(x.dtype) if need_dparams else None)
+    lib = L.load()
+    dx = torch.empty_like(x) if need_dx else None
+    dgm = torch.empty(d, dtype=x.dtype, device=x.device) if need_dparams else None
+    dbt = torch.empty(d, dtype=x.dtype, device=x.device) if need_dparams else None
+    scratch = None
+    if need_dparams:
+        scratch = torch.empty(max(int(lib.dg_layernorm_bwd_scratch_bytes(rows, d)), 4), dtype=torch.uint8,
+                              device=x.device)
+    L.check(lib.dg_layernorm_bwd(L.dtype_code(x.dtype), L.ptr(dx), L.ptr(dgm), L.ptr(dbt), g.data_ptr(), x.data_ptr(),
+                                 gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d, L.ptr(scratch),
+                                 L.stream_ptr()), "dg_layernorm_bwd")
+    _cnt((1 if need_dx else 0) + (2 if need_dparams else 0))
+    return dx, dgm, dbt
+
+
+# ----------------------------------------------------------------------------- embedding
+def index_from_float(idx: torch.Tensor, limit: int) -> torch.Tensor:
+    """Reference convention: indices arrive as float tensors. Returns int64, bounds-checked."""
+    if idx.dtype in (torch.int64, torch.int32):
+        out = idx.to(torch.int64).reshape(-1)
+        if out.numel() and not _is_cuda(out) and (out.min() < 0 or out.max() >= limit):
+            raise IndexError("index out of range")
+        return out
+    flat = idx.reshape(-1)
+    if not _is_cuda(flat):
+        out = flat.to(torch.int64)
+        if out.numel() and (out.min() < 0 or out.max() >= limit):
+            raise IndexError("index out of range")
+        return out
+    flat = contiguous(flat.float() if flat.dtype != torch.float32 else flat)
+    out = torch.empty(flat.numel(), dtype=torch.int64, device=flat.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=flat.device)
+    L.check(L.load().dg_index_from_float(out.data_ptr(), flat.data_ptr(), flat.numel(), limit, bad.data_ptr(),
+                                         L.stream_ptr()), "dg_index_from_float")
+    _cnt()
+    if int(bad.item()) != 0:
+        raise IndexError("index out of range")
+    return out
+
+
+def one_hot(idx: torch.Tensor, classes: int) -> torch.Tensor:
+    if not _is_cuda(idx):
+        return torch.nn.functional.one_hot(idx, classes).float()
+    out = torch.empty(idx.numel(), classes, dtype=torch.float32, device=idx.device)
+    L.check(L.load().dg_one_hot(out.data_ptr(), idx.data_ptr(), idx.numel(), classes, L.stream_ptr()), "dg_one_hot")
+    _cnt()
+    return out
+
+
+def embedding_fwd(table, idx, pos_table=None, pos_idx=None):
+    n, d = idx.numel(), table.shape[1]
+    if not _is_cuda(table):
+        out = table[idx]
+        if pos_table is not None:
+            out = out + pos_table[pos_idx]
+        return out
+    out = torch.empty(n, d, dtype=table.dtype, device=table.device)
+    L.check(L.load().dg_embedding_fwd(L.dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), idx.data_ptr(),
+                                      L.ptr(pos_table), L.ptr(pos_idx), n, d, table.shape[0], L.stream_ptr()),
+            "dg_embedding_fwd")
+    _cnt()
+    return out
+
+
+def embedding_bwd(g, idx, vocab, out: torch.Tensor | None = None):
+    """Scatter-add g [n, d] into a [vocab, d] gradient (zero-initialised when ``out`` is None)."""
+    n, d = g.shape
+    if out is None:
+        out = torch.zeros(vocab, d, dtype=g.dtype, device=g.device)
+    if not _is_cuda(g):
+        out.index_add_(0, idx, g)
+        return out
+    L.check(L.load().dg_embedding_bwd(L.dtype_code(g.dtype), out.data_ptr(), g.data_ptr(), idx.data_ptr(), n, d, vocab,
+                                      L.stream_ptr()), "dg_embedding_bwd")
+    _cnt()
+    return out
+
+
+# ----------------------------------------------------------------------------- fused cross-entropy
+def xent_fwd_bwd(logits: torch.Tensor, target: torch.Tensor, grad_scale: float, inplace: bool = False):
+    """logits [T, V] (row stride may exceed V). Returns (loss_rows fp32 [T], dlogits)."""
+    T, V = logits.shape
+    if not _is_cuda(logits):
+        lf = logits.float()
+        lse = torch.logsumexp(lf, dim=1)
+        loss_rows = lse - lf.gather(1, target.reshape(-1, 1)).squeeze(1)
+        p = torch.exp(lf - lse[:, None])
+        p[torch.arange(T), target] -= 1.0
+        return loss_rows, (p * grad_scale).to(logits.dtype)
+    assert logits.stride(1) == 1
+    ld = logits.stride(0)
+    loss_rows = torch.empty(T, dtype=torch.float32, device=logits.device)
+    dlogits = logits if inplace else torch.empty_strided(logits.shape, logits.stride(), dtype=logits.dtype,
+                                                         device=logits.device)
+    L.check(L.load().dg_xent_fwd_bwd(L.dtype_code(logits.dtype), loss_rows.data_ptr(), None, dlogits.data_ptr(),
+                                     logits.data_ptr(), target.data_ptr(), T, V, ld, float(grad_scale),
+                                     L.stream_ptr()), "dg_xent_fwd_bwd")
+    _cnt()
+    return loss_rows, dlogits
+
+
+# ----------------------------------------------------------------------------- optimizers / init
+def adam_step(p, master, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
+    if not _is_cuda(p):
+        gf = g.float() * grad_scale
+        m.mul_(beta1).add_(gf, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
+        mhat = m / (1 - beta1 ** step)
+        vhat = v / (1 - beta2 ** step)
+        base = master if master is not None else p
+        new = base.float() - lr * (mhat / (vhat.sqrt() + eps) + wd * base.float())
+        if master is not None:
+            master.copy_(new)
+        p.copy_(new.to(p.dtype))
+        return
+    L.check(L.load().dg_adam_step(L.dtype_code(p.dtype), p.data_ptr(), L.ptr(master), L.dtype_code(g.dtype),
+                                  g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), lr, beta1, beta2, eps, wd,
+                                  int(step), float(grad_scale), L.stream_ptr()), "dg_adam_step")
+    _cnt()
+
+
+def sgd_step(p, master, g, lr, grad_scale=1.0):
+    if not _is_cuda(p):
+        base = master if master is not None else p
+        new = base.float() - lr * grad_scale * g.float()
+        if master is not None:
+            master.copy_(new)
+        p.copy_(new.to(p.dtype))
+        return
+    L.check(L.load().dg_sgd_step(L.dtype_code(p.dtype), p.data_ptr(), L.ptr(master), L.dtype_code(g.dtype),
+                                 g.data_ptr(), p.numel(), float(lr), float(grad_scale), L.stream_ptr()), "dg_sgd_step")
+    _cnt()
+
+
+def randn_(t: torch.Tensor, seed: int, offset: int, mean: float = 0.0, std: float = 1.0, generator=None):
+    if not _is_cuda(t):
+        t.copy_((torch.randn(t.shape, generator=generator) * std + mean).to(t.dtype))
+        return t
+    L.check(L.load().dg_randn(L.dtype_code(t.dtype), t.data_ptr(), t.numel(), seed & (2 ** 64 - 1), offset, mean, std,
+                              L.stream_ptr()), "dg_randn")
+    _cnt()
+    return t
+
+
+def fill_(t: torch.Tensor, value: float):
+    if not _is_cuda(t):
+        t.fill_(value)
+        return t
+    assert t.is_contiguous()
+    L.check(L.load().dg_fill(L.dtype_code(t.dtype), t.data_ptr(), t.numel(), float(value), L.stream_ptr()), "dg_fill")
+    _cnt()
+    return t
+
+
+# ----------------------------------------------------------------------------- GEMM
+def _gemm_status_word(device) -> torch.Tensor:
+    st = _STATUS.get(device)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device] = st
+    return st
+
+
+_STATUS: dict = {}
+# "auto": tcgen05 for bf16 when the TMA rules hold, SIMT otherwise. "simt" forces the SIMT kernel.
+GEMM_BACKEND = "auto"
+
+
+def gemm_status(device=None) -> int:
+    """Non-zero if a bounded wait inside a tcgen05 kernel expired since the last call."""
+    total = 0
+    for dev, st in _STATUS.items():
+        if device is None or dev == device:
+            total |= int(st.item())
+            st.zero_()
+    return total
+
+
+def gemm2d(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, out_dtype=None, bias=None,
+           epi: int = 0, aux: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+           alpha: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """D = epilogue(alpha * op(a) @ op(b)) for (batched) 2-D operands.
+
+    ``a`` is [.., M, K] (or [.., K, M] with ``trans_a``), ``b`` is [.., K, N] (or [.., N, K] with
+    ``trans_b``); both row-major with the last dim contiguous; leading batch dims must match
+    (or be absent on one side = broadcast). Output [.., M, N] contiguous.
+    """
+    assert a.stride(-1) == 1 and b.stride(-1) == 1
+    M, K = (a.shape[-1], a.shape[-2]) if trans_a else (a.shape[-2], a.shape[-1])
+    Kb, N = (b.shape[-1], b.shape[-2]) if trans_b else (b.shape[-2], b.shape[-1])
+    if K != Kb:
+        raise RuntimeError(f"matmul inner dims differ: {K} vs {Kb}")
+    ba, bb = a.shape[:-2], b.shape[:-2]
+    batch_shape = ba if len(ba) >= len(bb) else bb
+    batch = math.prod(batch_shape)
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty(*batch_shape, M, N, dtype=out_dtype, device=a.device)
+    if not _is_cuda(a):
+        A = a.float().transpose(-1, -2) if trans_a else a.float()
+        Bm = b.float().transpose(-1, -2) if trans_b else b.float()
+        acc = alpha * (A @ Bm)
+        if bias is not None:
+            acc = acc + bias.float().reshape(-1)
+        if epi in (L.EPI_GELU, L.EPI_RELU):
+            if aux is not None:
+                aux.copy_(acc.to(aux.dtype))
+            acc = _gelu_cpu(acc) if epi == L.EPI_GELU else torch.clamp_min(acc, 0)
+        elif epi == L.EPI_DGELU:
+            acc = acc * _gelu_grad_cpu(aux.float())
+        elif epi == L.EPI_DRELU:
+            acc = torch.where(aux.float() > 0, acc, torch.zeros_like(acc))
+        if residual is not None:
+            acc = acc + residual.float()
+        out.copy_(acc.to(out.dtype))
+        return out
+
+    def bstride(t, bshape):
+        if len(bshape) == 0:
+            return 0
+        # batch dims must collapse to one stride
+        if math.prod(bshape) == 1:
+            return 0
+        tt = t.reshape(-1, t.shape[-2], t.shape[-1]) if t.is_contiguous() else None
+        if tt is None:
+            raise RuntimeError("batched GEMM operands must be contiguous over their batch dims")
+        return tt.stride(0)
+
+    a_bs, b_bs = bstride(a, ba), bstride(b, bb)
+    lib = L.load()
+    use_tc = (GEMM_BACKEND == "auto" and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+              and out.dtype in (torch.bfloat16, torch.float32))
+    if use_tc:
+        args = L.GemmArgs()
+        args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        args.bias = L.ptr(bias)
+        args.aux = L.ptr(aux)
+        args.residual = L.ptr(residual)
+        args.M, args.N, args.K, args.batch = M, N, K, batch
+        args.lda, args.ldb, args.ldd = a.stride(-2), b.stride(-2), N
+        args.a_bs, args.b_bs, args.d_bs = a_bs, b_bs, M * N
+        args.a_kmajor = 0 if trans_a else 1
+        args.b_kmajor = 1 if trans_b else 0
+        args.out_dtype = L.dtype_code(out.dtype)
+        args.bias_dtype = L.dtype_code(bias.dtype) if bias is not None else 0
+        args.epi = epi
+        args.alpha = alpha
+        args.status = _gemm_status_word(a.device).data_ptr()
+        if residual is not None:
+            assert residual.dtype == out.dtype and residual.is_contiguous()
+        if aux is not None:
+            assert aux.dtype == torch.bfloat16 and aux.is_contiguous()
+        if lib.dg_gemm_sm100_supported(C.byref(args)):
+            L.check(lib.dg_gemm_sm100(C.byref(args), L.stream_ptr()), "dg_gemm_sm100")
+            _cnt()
+            return out
+    # SIMT path (fp32, or bf16 shapes outside the TMA rules); epilogue pieces as separate kernels
+    if out.dtype != a.dtype:
+        tmp = torch.empty(out.shape, dtype=a.dtype, device=a.device)
+    else:
+        tmp = out
+    ars, acs = (1, a.stride(-2)) if trans_a else (a.stride(-2), 1)
+    brs, bcs = (1, b.stride(-2)) if trans_b else (b.stride(-2), 1)
+    L.check(lib.dg_gemm_simt(L.dtype_code(a.dtype), tmp.data_ptr(), a.data_ptr(), b.data_ptr(), batch, M, N, K, a_bs,
+                             ars, acs, b_bs, brs, bcs, M * N, N, float(alpha), 0.0, L.stream_ptr()), "dg_gemm_simt")
+    _cnt()
+    if bias is not None:
+        ew("ADD", tmp, cast(bias.reshape(-1), tmp.dtype), ymode=BC_ROW, out=tmp)
+    if epi in (L.EPI_GELU, L.EPI_RELU):
+        if aux is not None:
+            assign_(aux, tmp)
+        ew("GELU" if epi == L.EPI_GELU else "RELU", tmp, out=tmp)
+    elif epi in (L.EPI_DGELU, L.EPI_DRELU):
+        ew("GELU_BWD" if epi == L.EPI_DGELU else "RELU_BWD", tmp, cast(aux, tmp.dtype), out=tmp)
+    if residual is not None:
+        ew("ADD", tmp, cast(residual, tmp.dtype), out=tmp)
+    if tmp is not out:
+        assign_(out, tmp)
+    return out

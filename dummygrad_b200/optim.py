@@ -1,0 +1,153 @@
+"""Optimizers.
+
+``SGD(param, lr)`` and ``Adam(lr).step(param)`` keep the reference's per-tensor calling
+convention, defaults and update rule (src/optimizers.h:5-14, 17-60): state is created lazily
+per tensor, each tensor has its own step counter, bias-corrected moments,
+``p -= lr * mhat / (sqrt(vhat) + eps)``, no weight decay.
+
+``AdamW`` is the training-loop form used by the large configs: it owns a parameter list,
+keeps fp32 master weights and moments for bf16 parameters and updates every tensor in one
+multi-tensor kernel launch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import weakref
+from typing import Iterable
+
+import torch
+
+from . import _lib as L
+from .ops import kernels as K
+from .tensor import Tensor
+
+
+def SGD(param: Tensor, lr: float) -> None:  # noqa: N802 - reference name
+    """p -= lr * grad; no-op when the tensor has no gradient (src/optimizers.h:5-14)."""
+    if param.grad is None:
+        return
+    p = param.data
+    g = K.contiguous(param.grad.data)
+    if p.is_contiguous():
+        K.sgd_step(p, None, g, lr)
+    else:
+        tmp = K.contiguous(p)
+        K.sgd_step(tmp, None, g, lr)
+        K.strided_copy(p, tmp)
+
+
+class ParamState:
+    """Per-tensor Adam state (src/optimizers.h:17-22)."""
+
+    __slots__ = ("m", "v", "t", "master")
+
+    def __init__(self, like: torch.Tensor, keep_master: bool):
+        self.m = torch.zeros(like.shape, dtype=torch.float32, device=like.device)
+        self.v = torch.zeros(like.shape, dtype=torch.float32, device=like.device)
+        self.t = 0
+        self.master = None
+        if keep_master:
+            self.master = K.cast(K.contiguous(like), torch.float32)
+
+
+class Adam:
+    def __init__(self, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                 weight_decay: float = 0.0):
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+        self.state: "weakref.WeakKeyDictionary[Tensor, ParamState]" = weakref.WeakKeyDictionary()
+
+    def step(self, param: Tensor) -> None:
+        if param.grad is None:
+            return
+        st = self.state.get(param)
+        if st is None:
+            st = ParamState(param.data, keep_master=param.dtype != torch.float32)
+            self.state[param] = st
+        st.t += 1
+        p = param.data
+        g = K.contiguous(param.grad.data)
+        if not p.is_contiguous():
+            tmp = K.contiguous(p)
+            K.adam_step(tmp, st.master, g, st.m, st.v, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay,
+                        st.t)
+            K.strided_copy(p, tmp)
+            return
+        K.adam_step(p, st.master, g, st.m, st.v, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, st.t)
+
+
+class AdamW:
+    """Multi-tensor Adam/AdamW over a fixed parameter list (one kernel launch per step)."""
+
+    CHUNK = 65536
+
+    def __init__(self, params: Iterable[Tensor], lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
+                 eps: float = 1e-8, weight_decay: float = 0.0):
+        self.params = [p for p in params]
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+        self.state = [ParamState(p.data, keep_master=p.dtype != torch.float32) for p in self.params]
+        self.t = 0
+        self._table = None
+
+    def zero_grad(self) -> None:
+        for p in self.params:
+            p.zero_grad()
+
+    def _build_table(self, device):
+        recs = (L_AdamRec * len(self.params))()
+        chunks = []
+        for i, (p, st) in enumerate(zip(self.params, self.state)):
+            n = p.size()
+            for off in range(0, n, self.CHUNK):
+                chunks += [i, off]
+        self._recs_host = recs
+        self._chunks = torch.tensor(chunks, dtype=torch.int64, device=device)
+        self._recs_dev = torch.empty(C.sizeof(recs), dtype=torch.uint8, device=device)
+        self._table = True
+
+    def step(self, grad_scale: float = 1.0) -> None:
+        self.t += 1
+        active = [(p, st) for p, st in zip(self.params, self.state) if p.grad is not None]
+        if not active:
+            return
+        dev = self.params[0].data
+        if not dev.is_cuda or len({p.dtype for p, _ in active}) > 1 or len({p.grad.dtype for p, _ in active}) > 1 \
+                or len(active) != len(self.params) or any(not p.data.is_contiguous() for p, _ in active):
+            for p, st in active:
+                st.t = self.t
+                K.adam_step(p.data, st.master, K.contiguous(p.grad.data), st.m, st.v, self.lr, self.beta1, self.beta2,
+                            self.eps, self.weight_decay, self.t, grad_scale)
+            return
+        if self._table is None:
+            self._build_table(dev.device)
+        recs = self._recs_host
+        for i, (p, st) in enumerate(active):
+            st.t = self.t
+            g = K.contiguous(p.grad.data)
+            recs[i].p = p.data.data_ptr()
+            recs[i].master = st.master.data_ptr() if st.master is not None else None
+            recs[i].g = g.data_ptr()
+            recs[i].m = st.m.data_ptr()
+            recs[i].v = st.v.data_ptr()
+            recs[i].n = p.size()
+            recs[i].step = self.t
+        host = torch.frombuffer(bytearray(bytes(recs)), dtype=torch.uint8)
+        self._recs_dev.copy_(host, non_blocking=False)
+        p0 = self.params[0]
+        L.check(L.load().dg_adam_multi(L.dtype_code(p0.dtype), L.dtype_code(p0.grad.dtype), self._recs_dev.data_ptr(),
+                                       self._chunks.data_ptr(), self._chunks.numel() // 2, self.CHUNK, self.lr,
+                                       self.beta1, self.beta2, self.eps, self.weight_decay, float(grad_scale),
+                                       L.stream_ptr()), "dg_adam_multi")
+        K._cnt()
+
+
+class L_AdamRec(C.Structure):
+    _fields_ = [("p", C.c_void_p), ("master", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("n", C.c_int64), ("step", C.c_int32), ("pad", C.c_int32)]
+
+
+def clip_grad_value_(params: Iterable[Tensor], lo: float = -1.0, hi: float = 1.0) -> None:
+    """Clamp every gradient element to [lo, hi] (the value clipping of src/mars.cpp:242-249)."""
+    from .ops.functional import clamp_
+    for p in params:
+        if p.grad is not None:
+            clamp_(p.grad.data, lo, hi)

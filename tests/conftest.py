@@ -1,0 +1,28 @@
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
+
+
+@pytest.fixture(params=DEVICES)
+def device(request):
+    if request.param == "cuda" and not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device(request.param)
+
+
+@pytest.fixture(autouse=True)
+def _default_device_reset():
+    import dummygrad_b200 as dg
+    yield
+    dg.set_default_dtype(torch.float32)

@@ -1,0 +1,129 @@
+"""T4: the tcgen05 GEMM against a PyTorch fp32 reference: all four operand layouts, ragged
+edges, batches with a shared operand, every epilogue, fp32 and bf16 outputs."""
+import pytest
+import torch
+
+import dummygrad_b200 as dg
+from dummygrad_b200 import _lib as L
+from dummygrad_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, ta, tb):
+    A = a.float().transpose(-1, -2) if ta else a.float()
+    B = b.float().transpose(-1, -2) if tb else b.float()
+    return A @ B
+
+
+def _mk(shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _check(out, ref, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"rel err {err / scale:.3e}"
+
+
+SHAPES = [(128, 128, 64), (256, 256, 128), (128, 256, 512), (384, 512, 1024), (200, 136, 72), (1, 8, 8), (129, 264, 200),
+          (1024, 50304 // 8, 256), (4096, 1024, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K_", SHAPES)
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_layouts(M, N, K_, ta, tb):
+    torch.manual_seed(0)
+    if (ta and M % 8) or ((not tb) and N % 8) or K_ % 8:
+        pytest.skip("TMA stride alignment needs multiples of 8 here")
+    a = _mk((K_, M) if ta else (M, K_))
+    b = _mk((N, K_) if tb else (K_, N))
+    before = K.launch_count
+    out = K.gemm2d(a, b, trans_a=ta, trans_b=tb)
+    assert K.launch_count == before + 1
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    _check(out, _ref(a, b, ta, tb))
+
+
+def test_uses_tcgen05_path():
+    a, b = _mk((256, 128)), _mk((128, 256))
+    args = L.GemmArgs()
+    out = torch.empty(256, 256, device="cuda", dtype=torch.bfloat16)
+    args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.M, args.N, args.K, args.batch = 256, 256, 128, 1
+    args.lda, args.ldb, args.ldd = 128, 256, 256
+    args.a_kmajor, args.b_kmajor, args.out_dtype = 1, 0, L.BF16
+    args.alpha = 1.0
+    import ctypes
+    assert L.load().dg_gemm_sm100_supported(ctypes.byref(args)) == 1
+
+
+def test_fp32_out_and_alpha():
+    torch.manual_seed(1)
+    a, b = _mk((300, 520)), _mk((520, 264))
+    out = K.gemm2d(a, b, out_dtype=torch.float32, alpha=0.5)
+    assert out.dtype == torch.float32
+    _check(out, 0.5 * _ref(a, b, False, False), tol=5e-3)
+
+
+def test_epilogues():
+    torch.manual_seed(2)
+    M, N, Kd = 260, 392, 128
+    a, b = _mk((M, Kd), 0.5), _mk((Kd, N), 0.2)
+    bias = _mk((N,))
+    res = _mk((M, N))
+    ref = _ref(a, b, False, False) + bias.float()
+    out = K.gemm2d(a, b, bias=bias)
+    _check(out, ref)
+    aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = K.gemm2d(a, b, bias=bias, epi=L.EPI_GELU, aux=aux, residual=res)
+    gelu = torch.nn.functional.gelu(ref, approximate="tanh")
+    _check(aux, ref)
+    _check(out, gelu + res.float())
+    g = _mk((M, Kd))
+    w2 = _mk((N, Kd), 0.2)
+    out = K.gemm2d(g, w2, trans_b=True, epi=L.EPI_DGELU, aux=aux)
+    x = aux.float().requires_grad_(True)
+    torch.nn.functional.gelu(x, approximate="tanh").sum().backward()
+    _check(out, (g.float() @ w2.float().t()) * x.grad)
+    out = K.gemm2d(a, b, bias=bias, epi=L.EPI_RELU, aux=aux)
+    _check(out, torch.relu(ref))
+    bias32 = bias.float()
+    out = K.gemm2d(a, b, bias=bias32)
+    _check(out, ref)
+
+
+def test_batched_and_shared_operand():
+    torch.manual_seed(3)
+    a, b = _mk((6, 200, 64)), _mk((6, 64, 136))
+    _check(K.gemm2d(a, b), a.float() @ b.float())
+    # shared A (batch stride 0): x [T, d] times three stacked weights
+    x, w = _mk((300, 128)), _mk((3, 128, 128), 0.2)
+    _check(K.gemm2d(x, w), x.float() @ w.float())
+    # attention-like NT and TN batches
+    q, k = _mk((2, 4, 96, 64)), _mk((2, 4, 96, 64))
+    _check(K.gemm2d(q, k, trans_b=True), q.float() @ k.float().transpose(-1, -2))
+    _check(K.gemm2d(q, k, trans_a=True), q.float().transpose(-1, -2) @ k.float())
+
+
+def test_accumulate_into_output():
+    """residual may alias the output: D += A B."""
+    torch.manual_seed(4)
+    a, b = _mk((256, 192)), _mk((192, 256))
+    d = _mk((256, 256))
+    ref = d.float() + _ref(a, b, False, False)
+    K.gemm2d(a, b, residual=d, out=d)
+    _check(d, ref)
+
+
+def test_many_tiles_persistent_schedule():
+    """More tiles than SMs, several waves, both accumulator buffers and every smem stage reused."""
+    torch.manual_seed(5)
+    a, b = _mk((128 * 20, 320), 0.3), _mk((320, 256 * 9), 0.3)
+    _check(K.gemm2d(a, b), _ref(a, b, False, False))
+
+
+def test_odd_shapes_fall_back_to_simt():
+    a, b = _mk((33, 17)), _mk((17, 9))
+    _check(K.gemm2d(a, b), _ref(a, b, False, False))
