@@ -1,0 +1,46 @@
+// Peer-memory primitives shared by the fused compute+collective kernels: system-scope
+// flag signalling with bounded waits, and 16-byte loads/stores that are safe on memory
+// another GPU writes (no stale L1 lines, no non-coherent path).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dg {
+namespace peer {
+
+constexpr long long kFlagWaitCycles = 4000000000LL;  // about two seconds at 2 GHz
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer_16(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Spin until *flag >= epoch. Returns false when the cycle budget runs out; never traps.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long budget = kFlagWaitCycles) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (ld_acquire_sys(flag) >= epoch) return true;
+    __nanosleep(100);
+    if (clock64() - t0 > budget) return false;
+  }
+}
+
+}  // namespace peer
+}  // namespace dg

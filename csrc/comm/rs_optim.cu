@@ -1,0 +1,165 @@
+// F1 (+ the store half of F2): data-parallel gradient reduce-scatter fused with the sharded
+// optimizer update and the parameter all-gather, as ONE kernel per bucket over NVLink peer
+// memory.
+//
+// Every rank owns the slice [rank*shard_n, (rank+1)*shard_n) of a bucket. The kernel
+//   1. publishes "my gradients of this bucket are final" to every peer's flag pad and waits
+//      (bounded) for the same flag from every peer,
+//   2. pulls its slice of every peer's bf16 gradient bucket with 16-byte peer loads, sums in
+//      fp32 in a fixed rank order (deterministic), applies the 1/(world*accumulation) scale,
+//   3. runs Adam/AdamW or SGD on the fp32 master slice (moments stay local: ZeRO-1 layout),
+//   4. pushes the updated bf16 parameters straight into every rank's parameter buffer with
+//      16-byte peer stores (the all-gather), and
+//   5. the last CTA to finish publishes "my slice of this bucket has landed everywhere".
+// A rank starts its next forward only after it has seen flag 5 from every rank for every
+// bucket (dg_flags_wait). No host synchronisation, no NCCL call, no staging copy.
+//
+// The reference has no counterpart: its optimizer is a host loop over one tensor
+// (src/optimizers.h:32-59); the update rule here is the same.
+#include "../kernels/common.cuh"
+#include "peer.cuh"
+#include "../include/dgb200_comm.h"
+
+namespace dg {
+
+__global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
+  __shared__ int s_ok;
+  const int W = a.world;
+  int* my_pad = a.flag_ptrs[a.rank];
+  const int ready_base = a.bucket_id * W;
+  const int done_base = a.n_buckets * W + a.bucket_id * W;
+
+  // 1. publish readiness (one thread of the grid) and wait for every peer
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < W; ++r) peer::st_release_sys(a.flag_ptrs[r] + ready_base + a.rank, a.epoch);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < W && ok; ++r) ok = peer::wait_flag(my_pad + ready_base + r, a.epoch, a.wait_cycles) ? 1 : 0;
+    if (!ok && a.status) atomicExch(a.status, 0x100 | a.bucket_id);
+    s_ok = ok;
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+
+  if (ok) {
+    const int64_t nvec = a.shard_n / 8;  // shard_n is a multiple of 8 (16-byte slices)
+    const int64_t base = a.bucket_off + (int64_t)a.rank * a.shard_n;
+    const float bc1 = 1.f - powf(a.beta1, (float)a.step), bc2 = 1.f - powf(a.beta2, (float)a.step);
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t e0 = v * 8;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // 2. pull + reduce in rank order
+      for (int r = 0; r < W; ++r) {
+        const bf16* src = reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base + e0;
+        uint4 raw = (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : peer::ld_peer_16(src);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float2 f = __bfloat1622float2(h[k]);
+          acc[2 * k] += f.x; acc[2 * k + 1] += f.y;
+        }
+      }
+      // 3. optimizer on the fp32 master slice
+      float4 p0 = *reinterpret_cast<const float4*>(a.master + e0), p1 = *reinterpret_cast<const float4*>(a.master + e0 + 4);
+      float pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+      if (a.optimizer == 0) {
+        float4 m0 = *reinterpret_cast<const float4*>(a.m + e0), m1 = *reinterpret_cast<const float4*>(a.m + e0 + 4);
+        float4 v0 = *reinterpret_cast<const float4*>(a.v + e0), v1 = *reinterpret_cast<const float4*>(a.v + e0 + 4);
+        float mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float g = acc[k] * a.grad_scale;
+          mw[k] = a.beta1 * mw[k] + (1.f - a.beta1) * g;
+          vw[k] = a.beta2 * vw[k] + (1.f - a.beta2) * g * g;
+          pw[k] -= a.lr * ((mw[k] / bc1) / (sqrtf(vw[k] / bc2) + a.eps) + a.wd * pw[k]);
+        }
+        *reinterpret_cast<float4*>(a.m + e0) = make_float4(mw[0], mw[1], mw[2], mw[3]);
+        *reinterpret_cast<float4*>(a.m + e0 + 4) = make_float4(mw[4], mw[5], mw[6], mw[7]);
+        *reinterpret_cast<float4*>(a.v + e0) = make_float4(vw[0], vw[1], vw[2], vw[3]);
+        *reinterpret_cast<float4*>(a.v + e0 + 4) = make_float4(vw[4], vw[5], vw[6], vw[7]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pw[k] -= a.lr * a.grad_scale * acc[k];
+      }
+      *reinterpret_cast<float4*>(a.master + e0) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<float4*>(a.master + e0 + 4) = make_float4(pw[4], pw[5], pw[6], pw[7]);
+      // 4. push the bf16 slice to every rank's parameter buffer
+      uint4 outv;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(pw[2 * k], pw[2 * k + 1]);
+      for (int rr = 0; rr < W; ++rr) {
+        const int r = (a.rank + rr) % W;  // start with the local copy, then rotate over peers
+        bf16* dst = reinterpret_cast<bf16*>(a.param_ptrs[r]) + base + e0;
+        if (r == a.rank) *reinterpret_cast<uint4*>(dst) = outv;
+        else peer::st_peer_16(dst, outv);
+      }
+    }
+  }
+
+  // 5. last CTA publishes completion (also on failure, so that peers do not wait for nothing)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(a.counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *a.counter = 0;
+      __threadfence_system();
+      if (ok) {
+        for (int r = 0; r < W; ++r) peer::st_release_sys(a.flag_ptrs[r] + done_base + a.rank, a.epoch);
+      }
+    }
+  }
+}
+
+__global__ void flags_wait_kernel(const int* flags, int n, int epoch, int* status, long long wait_cycles) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (!peer::wait_flag(flags + i, epoch, wait_cycles)) {
+      if (status) atomicExch(status, 0x200 | i);
+    }
+  }
+}
+
+__global__ void flags_signal_kernel(int* const* pads, int world, int offset, int value) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    peer::st_release_sys(pads[threadIdx.x] + offset, value);
+  }
+}
+
+}  // namespace dg
+
+extern "C" int dg_rs_optim(const dg_rs_optim_args* a, cudaStream_t stream) {
+  if (!a || a->world < 1 || a->rank < 0 || a->rank >= a->world) return DG_ERR_BAD_ARG;
+  if (a->shard_n <= 0 || a->shard_n % 8 != 0 || a->bucket_off % 8 != 0) return DG_ERR_BAD_ARG;
+  if (!a->grad_ptrs || !a->param_ptrs || !a->flag_ptrs || !a->master || !a->counter) return DG_ERR_BAD_ARG;
+  if (a->optimizer == 0 && (!a->m || !a->v || a->step < 1)) return DG_ERR_BAD_ARG;
+  dg_rs_optim_args args = *a;
+  if (args.wait_cycles <= 0) args.wait_cycles = dg::peer::kFlagWaitCycles;
+  int64_t nvec = a->shard_n / 8;
+  int64_t want = (nvec + 256 * 4 - 1) / (256 * 4);
+  int cap = a->max_ctas > 0 ? a->max_ctas : 148 * 2;
+  int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  dg::rs_optim_kernel<<<blocks, 256, 0, stream>>>(args);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_flags_wait(const int* flags, int n, int epoch, int* status, long long wait_cycles,
+                             cudaStream_t stream) {
+  if (n <= 0) return DG_OK;
+  if (wait_cycles <= 0) wait_cycles = dg::peer::kFlagWaitCycles;
+  dg::flags_wait_kernel<<<1, 128, 0, stream>>>(flags, n, epoch, status, wait_cycles);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+extern "C" int dg_flags_signal(int* const* pads_dev, int world, int offset, int value, cudaStream_t stream) {
+  if (world < 1 || world > 32) return DG_ERR_BAD_ARG;
+  dg::flags_signal_kernel<<<1, 32, 0, stream>>>(pads_dev, world, offset, value);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}

@@ -1,0 +1,319 @@
+"""Data-parallel training with a sharded optimizer (ZeRO-1 layout) whose communication is the
+fused reduce-scatter + optimizer + all-gather kernel (``dg_rs_optim``), launched per bucket
+while backward is still running.
+
+Layout. All parameters live in one flat bf16 (or fp32) buffer, all gradients in a second flat
+buffer of the same layout; both are symmetric allocations every rank can address. The flat
+space is cut into buckets in reverse parameter order (the order in which backward finishes
+gradients); bucket ``b`` is split evenly over the ranks and rank ``r`` owns slice ``r``: fp32
+master weights and Adam moments exist only for owned slices.
+
+Step. The engine's leaf hook fires when a parameter's gradient is final. When the last
+parameter of a bucket reports, an event is recorded on the compute stream and the bucket's
+fused kernel is enqueued on the communication stream behind it: it handshakes with the peers
+through flag pads, pulls the owned slice of every peer's gradients over NVLink, updates the
+master slice and pushes the new bf16 parameters into every rank's parameter buffer. The next
+forward waits (on the device) for the "landed" flags of every bucket from every rank.
+
+``comm="collective"`` replaces the fused kernel by torch.distributed collectives
+(all-reduce, local update, all-gather): the NCCL baseline on GPUs and the only path on CPU
+(gloo), where the host-side logic (bucketing, sharding, hooks, accumulation) is tested.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib as L
+from ..ops import kernels as K
+from ..tensor import Tensor
+from .symm import SymmBuffer
+
+
+class RsOptimArgs(C.Structure):
+    _fields_ = [
+        ("grad_ptrs", C.c_void_p), ("param_ptrs", C.c_void_p), ("flag_ptrs", C.c_void_p),
+        ("master", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+        ("bucket_off", C.c_int64), ("shard_n", C.c_int64),
+        ("rank", C.c_int), ("world", C.c_int), ("bucket_id", C.c_int), ("n_buckets", C.c_int),
+        ("epoch", C.c_int), ("step", C.c_int),
+        ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float), ("wd", C.c_float),
+        ("grad_scale", C.c_float),
+        ("optimizer", C.c_int), ("counter", C.c_void_p), ("status", C.c_void_p), ("max_ctas", C.c_int),
+        ("wait_cycles", C.c_longlong),
+    ]
+
+
+def _bind_comm(lib):
+    if getattr(lib, "_dg_comm_bound", False):
+        return lib
+    lib.dg_rs_optim.argtypes = [C.POINTER(RsOptimArgs), C.c_void_p]
+    lib.dg_rs_optim.restype = C.c_int
+    lib.dg_flags_wait.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]
+    lib.dg_flags_wait.restype = C.c_int
+    lib.dg_flags_signal.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.dg_flags_signal.restype = C.c_int
+    lib._dg_comm_bound = True
+    return lib
+
+
+@dataclass
+class Bucket:
+    index: int
+    offset: int            # element offset in the flat buffers
+    numel: int             # padded size, multiple of 8 * world
+    params: list = field(default_factory=list)
+    pending: int = 0
+    launched: bool = False
+    state_off: int = 0     # offset of this bucket's owned slice in the master/moment buffers
+
+    def shard_n(self, world: int) -> int:
+        return self.numel // world
+
+
+def plan_buckets(sizes: list[int], world: int, bucket_elems: int, align: int = 8) -> tuple[list[tuple[int, int, list[int]]], list[int], int]:
+    """Lay parameters (given in bucket order) into a flat space.
+
+    Returns (buckets, param_offsets, total) where each bucket is (offset, padded_numel,
+    [param indices]); every parameter starts on a multiple of ``align`` elements and every
+    bucket size is a multiple of ``align * world`` so that rank slices are 16-byte aligned.
+    """
+    buckets, offsets = [], [0] * len(sizes)
+    cur_off, cur_len, cur_idx = 0, 0, []
+    total = 0
+    quantum = align * world
+
+    def close():
+        nonlocal cur_off, cur_len, cur_idx, total
+        if not cur_idx:
+            return
+        padded = (cur_len + quantum - 1) // quantum * quantum
+        buckets.append((cur_off, padded, cur_idx))
+        total = cur_off + padded
+        cur_off, cur_len, cur_idx = total, 0, []
+
+    for i, n in enumerate(sizes):
+        n_al = (n + align - 1) // align * align
+        if cur_idx and cur_len + n_al > bucket_elems:
+            close()
+        offsets[i] = cur_off + cur_len
+        cur_len += n_al
+        cur_idx.append(i)
+    close()
+    return buckets, offsets, total
+
+
+class DataParallel:
+    """Wraps a model for (data-parallel) training with the fused sharded optimizer.
+
+    ``step_done()`` must be called once per optimizer step after the last ``backward``; use
+    :class:`dummygrad_b200.parallel.trainer.Trainer` for the complete loop.
+    """
+
+    def __init__(self, model, *, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, optimizer="adamw",
+                 bucket_mb: float = 64.0, comm: str = "fused", group=None, max_comm_ctas: int = 32,
+                 wait_seconds: float = 20.0):
+        self.model = model
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        params = []
+        seen = set()
+        for p in model.parameters():
+            if id(p) not in seen:
+                seen.add(id(p))
+                params.append(p)
+        self.params = params
+        p0 = params[0]
+        self.device = p0.data.device
+        self.dtype = p0.dtype
+        assert all(p.dtype == self.dtype for p in params), "all parameters must share one dtype"
+        self.is_cuda = self.device.type == "cuda"
+        self.comm = comm if self.is_cuda else "collective"
+        if self.comm == "fused" and self.dtype != torch.bfloat16:
+            self.comm = "collective"  # the fused kernel moves bf16 gradients and parameters
+        self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=weight_decay)
+        self.optimizer = 0 if optimizer in ("adam", "adamw") else 1
+        self.max_comm_ctas = max_comm_ctas
+        self.wait_cycles = int(wait_seconds * 1.9e9)
+        self.t = 0
+        self.epoch = 0
+        self.accum_steps = 1
+        self._sync = True
+
+        # ---- flat layout, buckets in reverse parameter order
+        order = list(reversed(range(len(params))))
+        sizes = [params[i].size() for i in order]
+        esize = 2 if self.dtype == torch.bfloat16 else 4
+        plan, offs, total = plan_buckets(sizes, self.world, max(int(bucket_mb * 2 ** 20 / esize), 8 * self.world))
+        self.total = total
+        if self.comm == "fused":
+            self.param_buf = SymmBuffer(total, self.dtype, self.device, group)
+            self.grad_buf = SymmBuffer(total, self.dtype, self.device, group)
+        else:
+            self.param_buf = SymmBuffer.__new__(SymmBuffer)
+            self.param_buf.tensor = torch.zeros(total, dtype=self.dtype, device=self.device)
+            self.grad_buf = SymmBuffer.__new__(SymmBuffer)
+            self.grad_buf.tensor = torch.zeros(total, dtype=self.dtype, device=self.device)
+        self.param_flat, self.grad_flat = self.param_buf.tensor, self.grad_buf.tensor
+        self.buckets: list[Bucket] = []
+        self._bucket_of: dict[int, Bucket] = {}
+        state_off = 0
+        for bi, (off, numel, idxs) in enumerate(plan):
+            b = Bucket(bi, off, numel, [params[order[j]] for j in idxs], state_off=state_off)
+            state_off += numel // self.world
+            self.buckets.append(b)
+        for j, i in enumerate(order):
+            p = params[i]
+            n = p.size()
+            view = self.param_flat[offs[j]:offs[j] + n].view(p.data.shape)
+            K.strided_copy(view, p.data)
+            p.data = view
+            p.set_grad_sink(self.grad_flat[offs[j]:offs[j] + n].view(p.data.shape))
+            p.register_post_accumulate_hook(self._on_grad_ready)
+        for b in self.buckets:
+            for p in b.params:
+                self._bucket_of[id(p)] = b
+        # ---- owned optimizer state
+        self.master = torch.empty(state_off, dtype=torch.float32, device=self.device)
+        self.m = torch.zeros(state_off, dtype=torch.float32, device=self.device) if self.optimizer == 0 else None
+        self.v = torch.zeros(state_off, dtype=torch.float32, device=self.device) if self.optimizer == 0 else None
+        for b in self.buckets:
+            sn = b.shard_n(self.world)
+            lo = b.offset + self.rank * sn
+            K.assign_(self.master[b.state_off:b.state_off + sn], self.param_flat[lo:lo + sn])
+        # ---- fused-path resources
+        if self.comm == "fused":
+            nb = len(self.buckets)
+            self.flags = SymmBuffer(2 * nb * self.world, torch.int32, self.device, group)
+            self.counters = torch.zeros(nb, dtype=torch.int32, device=self.device)
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.comm_stream = torch.cuda.Stream(self.device)
+            self.lib = _bind_comm(L.load())
+        if dist.is_initialized():
+            dist.barrier(group)
+
+    # ------------------------------------------------------------------ step control
+    def begin_step(self, accum_steps: int = 1) -> None:
+        """Call before the first forward of an optimizer step."""
+        self.accum_steps = accum_steps
+        self.t += 1
+        self.epoch += 1
+        for b in self.buckets:
+            b.pending = len(b.params)
+            b.launched = False
+        for p in self.params:
+            p.zero_grad()
+
+    def set_sync(self, sync: bool) -> None:
+        """False during all but the last micro-batch of a step: gradients only accumulate."""
+        self._sync = sync
+        if sync:
+            for b in self.buckets:
+                b.pending = len(b.params)
+
+    def _on_grad_ready(self, p: Tensor) -> None:
+        if not self._sync:
+            return
+        b = self._bucket_of[id(p)]
+        b.pending -= 1
+        if b.pending == 0 and not b.launched:
+            self._launch(b)
+
+    def _launch(self, b: Bucket) -> None:
+        b.launched = True
+        if self.comm != "fused":
+            return  # collectives run in finish_step
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.comm_stream.wait_event(ev)
+        a = RsOptimArgs()
+        a.grad_ptrs = self.grad_buf.ptrs_dev.data_ptr()
+        a.param_ptrs = self.param_buf.ptrs_dev.data_ptr()
+        a.flag_ptrs = self.flags.ptrs_dev.data_ptr()
+        sn = b.shard_n(self.world)
+        a.master = self.master.data_ptr() + 4 * b.state_off
+        a.m = self.m.data_ptr() + 4 * b.state_off if self.m is not None else None
+        a.v = self.v.data_ptr() + 4 * b.state_off if self.v is not None else None
+        a.bucket_off, a.shard_n = b.offset, sn
+        a.rank, a.world, a.bucket_id, a.n_buckets = self.rank, self.world, b.index, len(self.buckets)
+        a.epoch, a.step = self.epoch, self.t
+        a.lr, a.beta1, a.beta2, a.eps, a.wd = (self.hp["lr"], self.hp["beta1"], self.hp["beta2"], self.hp["eps"],
+                                                self.hp["wd"])
+        a.grad_scale = 1.0 / (self.world * self.accum_steps)
+        a.optimizer = self.optimizer
+        a.counter = self.counters.data_ptr() + 4 * b.index
+        a.status = self.status.data_ptr()
+        a.max_ctas = self.max_comm_ctas
+        a.wait_cycles = self.wait_cycles
+        L.check(self.lib.dg_rs_optim(C.byref(a), self.comm_stream.cuda_stream), "dg_rs_optim")
+        K._cnt()
+
+    def finish_step(self) -> None:
+        """Call after the last backward of an optimizer step: flush buckets whose parameters got no
+        gradient, then make the next forward wait for every rank's parameter pushes."""
+        for b in self.buckets:
+            if not b.launched:
+                for p in b.params:
+                    if not p._sink_filled:
+                        K.fill_(p._grad_sink, 0.0)
+                        p._sink_filled = True
+                self._launch(b)
+        if self.comm == "fused":
+            nb = len(self.buckets)
+            done = self.flags.tensor.data_ptr() + 4 * nb * self.world
+            L.check(self.lib.dg_flags_wait(done, nb * self.world, self.epoch, self.status.data_ptr(), self.wait_cycles,
+                                           self.comm_stream.cuda_stream), "dg_flags_wait")
+            K._cnt()
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+            return
+        self._collective_update()
+
+    def _collective_update(self) -> None:
+        scale = 1.0 / (self.world * self.accum_steps)
+        for b in self.buckets:
+            g = self.grad_flat[b.offset:b.offset + b.numel]
+            if self.world > 1:
+                if g.dtype == torch.bfloat16 and not self.is_cuda:
+                    gf = g.float()
+                    dist.all_reduce(gf, group=self.group)
+                    g.copy_(gf.to(g.dtype))
+                else:
+                    dist.all_reduce(g, group=self.group)
+            sn = b.shard_n(self.world)
+            lo = b.offset + self.rank * sn
+            pshard = self.param_flat[lo:lo + sn]
+            ms = self.master[b.state_off:b.state_off + sn]
+            if self.optimizer == 0:
+                K.adam_step(pshard, ms, self.grad_flat[lo:lo + sn], self.m[b.state_off:b.state_off + sn],
+                            self.v[b.state_off:b.state_off + sn], self.hp["lr"], self.hp["beta1"], self.hp["beta2"],
+                            self.hp["eps"], self.hp["wd"], self.t, scale)
+            else:
+                K.sgd_step(pshard, ms, self.grad_flat[lo:lo + sn], self.hp["lr"], scale)
+            if self.world > 1:
+                full = self.param_flat[b.offset:b.offset + b.numel]
+                if full.dtype == torch.bfloat16 and not self.is_cuda:
+                    parts = [torch.empty(sn, dtype=torch.float32) for _ in range(self.world)]
+                    dist.all_gather(parts, pshard.float(), group=self.group)
+                    full.copy_(torch.cat(parts).to(full.dtype))
+                else:
+                    dist.all_gather_into_tensor(full, pshard.clone(), group=self.group)
+
+    def check_status(self) -> int:
+        """Non-zero when a bounded wait inside a fused kernel expired (reads the device word)."""
+        if self.comm != "fused":
+            return 0
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+        return code
+
+    # ------------------------------------------------------------------ checkpoint support
+    def owned_state(self) -> dict:
+        return {"master": self.master, "m": self.m, "v": self.v, "t": self.t,
+                "buckets": [(b.offset, b.numel, b.state_off) for b in self.buckets], "world": self.world,
+                "rank": self.rank}

@@ -1,0 +1,91 @@
+"""T5: data-parallel host logic on CPU ranks (gloo): bucket planning, sharded optimizer state,
+gradient accumulation, and step parity between 1 rank and 2 ranks on the same global batch."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import dummygrad_b200 as dg
+from dummygrad_b200.parallel.dp import plan_buckets
+
+
+def test_plan_buckets_alignment():
+    sizes = [10, 64, 7, 1000, 3]
+    for world in (1, 2, 4, 8):
+        buckets, offs, total = plan_buckets(sizes, world, 128)
+        assert total % (8 * world) == 0
+        covered = 0
+        for off, numel, idx in buckets:
+            assert off == covered and numel % (8 * world) == 0
+            covered += numel
+            for i in idx:
+                assert off <= offs[i] and offs[i] + sizes[i] <= off + numel and offs[i] % 8 == 0
+        assert covered == total
+        assert sorted(i for _, _, idx in buckets for i in idx) == list(range(len(sizes)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run_rank(rank, world, port, ids, tgt, steps, micro, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    dg.set_default_device("cpu")
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dummygrad_b200.parallel.trainer import Trainer
+    dg.manual_seed(0)
+    model = dg.GPT(64, 16, 32, 2, 2, device=torch.device("cpu"))
+    tr = Trainer(model, micro_batch=micro, lr=1e-2, bucket_mb=0.02, comm="collective")
+    B = ids.shape[0] // world
+    S = ids.shape[1]
+    my_ids = ids[rank * B:(rank + 1) * B]
+    my_tgt = tgt.reshape(-1, S)[rank * B:(rank + 1) * B].reshape(-1)
+    losses = []
+    for _ in range(steps):
+        l = torch.tensor([tr.step(my_ids, my_tgt)])
+        if world > 1:
+            dist.all_reduce(l)
+            l /= world
+        losses.append(float(l))
+    if rank == 0:
+        out.put((losses, model.token_emb.weight.data.flatten().tolist(), len(tr.dp.buckets)))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _launch(world, ids, tgt, steps, micro):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run_rank, args=(r, world, port, ids, tgt, steps, micro, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return res
+
+
+@pytest.mark.timeout(600)
+def test_dp_two_ranks_match_one_rank():
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (8, 16))
+    tgt = torch.randint(0, 64, (8 * 16,))
+    l1, w1, nb = _launch(1, ids, tgt, 3, 4)     # one rank, 2 micro-batches of 4
+    l2, w2, _ = _launch(2, ids, tgt, 3, 2)      # two ranks, 2 micro-batches of 2 each
+    assert nb > 1, "test should exercise several buckets"
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(a)), (l1, l2)
+    assert max(abs(a - b) for a, b in zip(w1, w2)) < 1e-4
+    assert l1[-1] < l1[0]
