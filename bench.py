@@ -1,0 +1,302 @@
+"""Headline benchmark: training tokens per second of a GPT-style decoder on N B200 GPUs.
+
+    python bench.py --gpus N --steps K --warmup W [--config gpt350m|gpt1p3b|toy|mlp] [--impl ours|reference]
+
+The default configuration is the 350M decoder (vocab 50304, d_model 1024, 24 layers, 16 heads,
+FFN 4096, sequence 1024, global batch 64, bf16 compute with fp32 master weights, AdamW, uniform
+random tokens, random-initialised weights), data-parallel over N GPUs with the fused
+reduce-scatter + optimizer + all-gather kernel. The global batch is fixed, so this is strong
+scaling. One JSON line is printed by rank 0.
+
+Timed region: K optimizer steps, bracketed by a barrier and torch.cuda.synchronize on both
+sides, timed with CUDA events on the launching stream, maximum over ranks. `value` is measured
+on device-resident inputs; `e2e` repeats the measurement through Trainer.step, which copies the
+step's token ids and targets from pinned host memory and reads the loss back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (preset, global_batch, seq_len, micro_batch, dtype, lr)
+    "gpt350m": ("gpt350m", 64, 1024, 8, "bf16", 3e-4),
+    "gpt1p3b": ("gpt1p3b", 32, 2048, 2, "bf16", 2e-4),
+    "toy": ("toy", 8, 32, 8, "fp32", 3e-4),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def baseline_value(config: str):
+    """Published reference number for this metric/config (the reference publishes none)."""
+    return None
+
+
+def run_ours(args) -> dict:
+    import torch
+    import dummygrad_b200 as dg
+    from dummygrad_b200.ops import kernels as K
+    from dummygrad_b200.parallel import dist as D
+    from dummygrad_b200.parallel.trainer import Trainer
+
+    rank, world, device = D.init()
+    assert world == args.gpus or world == 1 and args.gpus == 1, f"launched {world} ranks for --gpus {args.gpus}"
+    assert device.type == "cuda", "bench.py needs a GPU"
+    dg.set_default_device(device)
+    preset, gbatch, seq, micro, dtype_name, lr = CONFIGS[args.config]
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    if args.micro_batch:
+        micro = args.micro_batch
+    assert gbatch % world == 0, "global batch must divide over the ranks"
+    lbatch = gbatch // world
+    micro = min(micro, lbatch)
+    dg.manual_seed(1234)   # same seed on every rank: identical initial weights
+    model = dg.models.build_preset(preset, dtype=dtype, device=device)
+    trainer = Trainer(model, micro_batch=micro, lr=lr, weight_decay=0.1 if args.config != "toy" else 0.0,
+                      comm=args.comm, bucket_mb=args.bucket_mb)
+    vocab = model.vocab_size
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_sets = 4
+    host_ids = [torch.randint(0, vocab, (lbatch, seq), generator=gen).pin_memory() for _ in range(n_sets)]
+    host_tgt = [torch.randint(0, vocab, (lbatch * seq,), generator=gen).pin_memory() for _ in range(n_sets)]
+    dev_ids = [t.to(device) for t in host_ids]
+    dev_tgt = [t.to(device) for t in host_tgt]
+
+    def timed(step_fn, steps, warmup):
+        for i in range(warmup):
+            step_fn(i)
+        torch.cuda.synchronize()
+        D.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device.index or 0)
+        sampler.start()
+        l0 = K.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step_fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        D.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        launches = K.launch_count - l0
+        return D.max_over_ranks(ms, device), clocks, launches
+
+    losses = []
+
+    def dev_step(i):
+        losses.append(trainer.step_device(dev_ids[i % n_sets], dev_tgt[i % n_sets]))
+
+    def e2e_step(i):
+        trainer.step(host_ids[i % n_sets], host_tgt[i % n_sets])
+
+    ms, clocks, launches = timed(dev_step, args.steps, args.warmup)
+    trainer.check()
+    first, last = float(losses[0].item()), float(losses[-1].item())
+    ms_e2e, _, _ = timed(e2e_step, args.steps, max(1, min(args.warmup, 2)))
+    trainer.check()
+    tokens = gbatch * seq
+    value = tokens * args.steps / (ms / 1e3)
+    e2e = tokens * args.steps / (ms_e2e / 1e3)
+    base = baseline_value(args.config)
+    out = {
+        "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / base) if base else None,
+        "dtype": dtype_name, "data": "synthetic uniform random tokens, random-init weights", "impl": "ours",
+        "config": {"model": preset, "global_batch": gbatch, "seq_len": seq, "micro_batch": micro,
+                   "parallelism": f"dp{world}", "optimizer": "adamw (fp32 master, sharded)", "comm": trainer.dp.comm,
+                   "l2": "no explicit flush: each step streams >10 GB of weights and activations (L2 is 126 MB)"},
+        "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": int(host_ids[0].numel() * 8 + host_tgt[0].numel() * 8),
+                "d2h_bytes_per_step": 4},
+        "loss_first": first, "loss_last": last, "params": model.num_parameters(),
+    }
+    D.barrier()
+    D.shutdown()
+    return out if rank == 0 else {}
+
+
+def run_mlp_ours(args) -> dict:
+    """Configuration 1 on one GPU: 784 -> 128 ReLU -> 10, batch 64, SGD 1e-2 (metric: samples/s)."""
+    import torch
+    import dummygrad_b200 as dg
+    from dummygrad_b200.ops import kernels as K
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    dg.set_default_device(device)
+    dg.manual_seed(0)
+    model = dg.MLP(device=device)
+    gen = torch.Generator().manual_seed(0)
+    hx = torch.randn(64, 784, generator=gen).pin_memory()
+    hy = torch.randint(0, 10, (64,), generator=gen).pin_memory()
+    dx = dg.Tensor.from_torch(hx.to(device))
+    dy = hy.to(device)
+    params = model.parameters()
+
+    def one(x, y):
+        model.zero_grad()
+        loss = model.loss(x, y)
+        loss.backward()
+        for p in params:
+            dg.SGD(p, 1e-2)
+        return loss
+
+    def run(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        l0 = K.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), sampler.stop(), K.launch_count - l0
+
+    stage_x = torch.empty(64, 784, device=device)
+    stage_y = torch.empty(64, dtype=torch.int64, device=device)
+
+    def e2e():
+        stage_x.copy_(hx, non_blocking=True)
+        stage_y.copy_(hy, non_blocking=True)
+        return one(dg.Tensor.from_torch(stage_x), stage_y).item()
+
+    ms, clocks, launches = run(lambda: one(dx, dy), args.steps, args.warmup)
+    ms2, _, _ = run(e2e, args.steps, args.warmup)
+    return {"metric": "train samples/sec (device-timed)", "value": 64 * args.steps / (ms / 1e3), "unit": "samples/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+            "data": "synthetic N(0,1) inputs, uniform labels, random-init weights", "impl": "ours",
+            "config": {"model": "mlp 784-128-10", "global_batch": 64, "seq_len": 1, "parallelism": "dp1",
+                       "l2": "launch-bound toy config; working set fits L2 (stated, not flushed)"},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": 64 * args.steps / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
+                    "h2d_bytes_per_step": 64 * 784 * 4 + 64 * 8, "d2h_bytes_per_step": 4}}
+
+
+def run_reference(args) -> dict:
+    """Times the unmodified reference headers (baseline/_ref/src) through their own API. The
+    reference is a single-threaded CPU library, so only the two small configurations can run."""
+    ref_src = os.path.join(ROOT, "baseline", "_ref", "src")
+    if not os.path.isdir(ref_src):
+        if os.path.isdir("/root/reference/src"):
+            import shutil
+            shutil.copytree("/root/reference/src", ref_src)
+        else:
+            return {"impl": "reference", "unavailable": "reference headers not present under baseline/_ref/src"}
+    if args.config in ("gpt350m", "gpt1p3b"):
+        return {"impl": "reference",
+                "unavailable": "reference is a single-threaded fp32 CPU header library with no GPU or distributed path: "
+                               "one step of this config is >1e17 FLOP at ~1 GFLOP/s (years); run --config toy or mlp"}
+    harness = "ref_toy.cpp" if args.config == "toy" else "ref_mlp.cpp"
+    exe = os.path.join(ROOT, "build", harness.replace(".cpp", ""))
+    os.makedirs(os.path.dirname(exe), exist_ok=True)
+    cc = subprocess.run(["g++", "-O3", "-march=native", "-std=c++20", "-I", ref_src,
+                         os.path.join(ROOT, "baseline", harness), "-o", exe], capture_output=True, text=True)
+    if cc.returncode != 0:
+        return {"impl": "reference", "unavailable": "g++ failed on the reference harness: " + cc.stderr[-200:].replace("\n", " ")}
+    t0 = time.time()
+    r = subprocess.run([exe, str(args.steps), str(args.warmup)], capture_output=True, text=True, timeout=3000)
+    if r.returncode != 0:
+        return {"impl": "reference", "unavailable": f"reference harness exited {r.returncode}"}
+    ms, per_s, first, last = r.stdout.split()[:4]
+    toy = args.config == "toy"
+    return {"metric": "train tokens/sec" if toy else "train samples/sec", "value": float(per_s),
+            "unit": "tokens/s" if toy else "samples/s", "n_gpus": 0, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": float(ms), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp32", "data": "synthetic", "impl": "reference",
+            "config": {"model": args.config, "device": "host CPU, one thread (the reference has no GPU path)",
+                       "wall_s": time.time() - t0}, "loss_first": first, "loss_last": last}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="gpt350m", choices=["gpt350m", "gpt1p3b", "toy", "mlp"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default="fused", choices=["fused", "collective"])
+    ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--bucket-mb", type=float, default=64.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(run_reference(args)), flush=True)
+        return
+    out = run_mlp_ours(args) if args.config == "mlp" else run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,78 @@
+"""Microbenchmark of the tcgen05 GEMM against cuBLAS (torch.matmul) on the same shapes.
+
+    python bench/gemm_bench.py [--shapes 8192x8192x8192,...] [--iters 20] [--layout nn|nt|tn]
+
+Timing: CUDA events on the launching stream, warm-up first, operands rotated through a pool
+larger than the 126 MB L2 so that every timed launch reads from HBM. Prints one JSON line per
+shape with achieved TFLOP/s and the fraction of the measured cuBLAS peak (MEASURED_PEAKS.json
+when present, else the stated fallback of 1590 TFLOP/s).
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from dummygrad_b200.ops import kernels as K  # noqa: E402
+
+
+def peak_tflops():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops", 1590.0), "measured"
+    return 1590.0, "fallback"
+
+
+def time_fn(fn, n_pool, iters, warmup=3):
+    for i in range(warmup):
+        fn(i % n_pool)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % n_pool)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="8192x8192x8192,4096x4096x4096,8192x1024x1024,8192x4096x1024,8192x1024x4096,8192x50304x1024")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--layout", default="nn")
+    ap.add_argument("--no-cublas", action="store_true")
+    a = ap.parse_args()
+    peak, src = peak_tflops()
+    ta, tb = a.layout[0] == "t", a.layout[1] == "t"
+    for s in a.shapes.split(","):
+        M, N, Kd = (int(v) for v in s.split("x"))
+        bytes_per_set = 2 * (M * Kd + Kd * N + M * N)
+        n_pool = max(2, min(8, int(400e6 // bytes_per_set) + 1))
+        As = [torch.randn((Kd, M) if ta else (M, Kd), device="cuda").to(torch.bfloat16) for _ in range(n_pool)]
+        Bs = [torch.randn((N, Kd) if tb else (Kd, N), device="cuda").to(torch.bfloat16) for _ in range(n_pool)]
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_fn(lambda i: K.gemm2d(As[i], Bs[i], trans_a=ta, trans_b=tb, out=out), n_pool, a.iters)
+        ref = (As[0].float().t() if ta else As[0].float()) @ (Bs[0].float().t() if tb else Bs[0].float()) if M * N * Kd <= 2 ** 33 else None
+        K.gemm2d(As[0], Bs[0], trans_a=ta, trans_b=tb, out=out)
+        err = ((out.float() - ref).abs().max() / ref.abs().max()).item() if ref is not None else None
+        rec = {"shape": [M, N, Kd], "layout": a.layout, "ms": ms, "tflops": 2.0 * M * N * Kd / ms / 1e9,
+               "rel_err": err, "status": K.gemm_status()}
+        rec["frac_of_peak"] = rec["tflops"] / peak
+        rec["peak_source"] = src
+        if not a.no_cublas:
+            def cub(i):
+                A = As[i].t() if ta else As[i]
+                Bm = Bs[i].t() if tb else Bs[i]
+                torch.matmul(A, Bm, out=out)
+            msc = time_fn(cub, n_pool, a.iters)
+            rec["cublas_ms"] = msc
+            rec["cublas_tflops"] = 2.0 * M * N * Kd / msc / 1e9
+        print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    main()
