@@ -1,0 +1,54 @@
+"""Per-kernel device-time breakdown of one training step of a GPT preset (1 GPU).
+
+    python bench/step_profile.py [--config gpt350m] [--micro-batch 8] [--batch 8]
+
+Prints the op-level profiler table and the host wall time of the step, which together show
+whether the step is bound by the GPU or by host-side dispatch.
+"""
+import argparse
+import os
+import sys
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import dummygrad_b200 as dg  # noqa: E402
+from dummygrad_b200.parallel.trainer import Trainer  # noqa: E402
+from dummygrad_b200.utils.profiler import profile  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="gpt350m")
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=0)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    dg.set_default_device(dev)
+    dg.manual_seed(0)
+    model = dg.models.build_preset(a.config, dtype=torch.bfloat16, device=dev)
+    seq = a.seq or model.max_seq_len
+    tr = Trainer(model, micro_batch=a.micro_batch)
+    ids = torch.randint(0, model.vocab_size, (a.batch, seq), device=dev)
+    tgt = torch.randint(0, model.vocab_size, (a.batch * seq,), device=dev)
+    for _ in range(2):
+        tr.step_device(ids, tgt)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    tr.step_device(ids, tgt)
+    e1.record()
+    t_host = time.time() - t0
+    torch.cuda.synchronize()
+    print(f"step: device {e0.elapsed_time(e1):.2f} ms, host enqueue {t_host * 1e3:.2f} ms, "
+          f"tokens {a.batch * seq}, peak mem {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB")
+    with profile() as prof:
+        tr.step_device(ids, tgt)
+    print(prof.report())
+
+
+if __name__ == "__main__":
+    main()
