@@ -1,0 +1,40 @@
+// Allocation-free variant of the column reduction (no counterpart in the reference, which
+// has no device code at all).
+//
+// Who needs it: callers that must not allocate device memory at the moment of the call -
+// code running inside a stream-ordered region that forbids cudaMalloc, a real-time or
+// fault-handling path that may not block on the allocator, or a host application that gave
+// the whole GPU memory budget to its own pool and cannot let a library take more.
+// dg_reduce_cols() asks its caller for a scratch buffer; this entry point brings its own.
+#pragma once
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Upper bound, in bytes, of the scratch the reduction may need through this entry point.
+#define DG_NOALLOC_SCRATCH_BYTES (4u << 20)
+
+// Same result as dg_reduce_cols(dtype, out, mean_out, x, B, R, C, mode, scratch, stream):
+// x [B, R, C] contiguous -> out [B, C] (mode: 0 sum, 1 mean, 2 biased variance, 3 its square
+// root; mean_out [B, C] is required for modes 2 and 3 and may be null otherwise).
+//
+// The scratch lives in one fixed array inside the library (DG_NOALLOC_SCRATCH_BYTES per GPU
+// that loads the library, held until the process exits). The call allocates and frees nothing,
+// on the host or on the device. Shapes whose scratch need exceeds the bound are rejected with
+// DG_ERR_TOO_LARGE (-4) before anything is launched: dg_reduce_cols_scratch_bytes(B, R, C)
+// tells the need in advance.
+//
+// The first call on each device looks up the array's device address; make that first call
+// outside any stream capture. Every call on a device shares the one array: two calls whose
+// kernels can overlap on the GPU (different streams without an ordering between them) race on
+// it, so order them. Nothing in the array has to start at zero - each call overwrites what it
+// reads - and its contents after a call are unspecified.
+int dg_reduce_cols_noalloc(int dtype, void* out, void* mean_out, const void* x, int64_t B, int64_t R,
+                           int64_t C, int mode, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,46 @@
+// Column reduction for callers that cannot allocate (see dgb200_noalloc.h): the two-stage
+// reduction of reduce.cu, run with its per-split partial sums in a fixed device array that is
+// part of this library's image instead of a buffer supplied by the caller.
+#include <cuda_runtime.h>
+#include "../include/dgb200.h"
+#include "../include/dgb200_noalloc.h"
+
+namespace {
+
+// The scratch itself. In host code this name is only a handle for the runtime's symbol table,
+// not an address a kernel could use, so the launcher below asks the runtime for the real
+// device address once per device and passes that pointer on.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DG_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of the array on the current device (looked up on the first call per device).
+int scratch_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return DG_ERR_BAD_ARG;
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return DG_OK;
+}
+
+}  // namespace
+
+extern "C" int dg_reduce_cols_noalloc(int dtype, void* out, void* mean_out, const void* x, int64_t B, int64_t R,
+                                      int64_t C, int mode, cudaStream_t stream) {
+  if (B == 0 || C == 0) return DG_OK;
+  if (B < 0 || C < 0 || R <= 0 || !out || !x) return DG_ERR_BAD_ARG;
+  const int64_t need = dg_reduce_cols_scratch_bytes(B, R, C);
+  if (need > (int64_t)DG_NOALLOC_SCRATCH_BYTES) return DG_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);
+  if (rc != DG_OK) return rc;
+  return dg_reduce_cols(dtype, out, mean_out, x, B, R, C, mode, scratch, stream);
+}
