@@ -1,0 +1,387 @@
+// K3 (backward): fused attention backward on tcgen05 tensor cores.
+//
+// One CTA per (128-key tile j, head, batch); it keeps K_j and V_j in shared memory and the
+// dK_j / dV_j accumulators in TMEM, and walks over the query tiles i that attend to it:
+//     S  = Q_i K_j^T                  P  = exp2(S * scale*log2e - LSE_i * log2e)     (recomputed, never stored)
+//     dP = dO_i V_j^T                 dS = P * (dP - Delta_i) * scale
+//     dV_j += P^T dO_i                dK_j += dS^T Q_i                dQ_i += dS K_j
+// Five MMAs per (i, j). The same shared-memory tiles serve as K-major and as MN-major operands
+// (a 128-byte-swizzled [rows][64] tile can be read either way through the UMMA descriptor), so
+// nothing is transposed. dQ partial tiles are added to an fp32 [B, S, H*dk] accumulator with
+// red.global.add.f32 and converted once at the end; Delta_i = rowsum(dO_i * O_i) comes from a
+// small pre-pass. Replaces the five separate ops, each with its own S x S gradient buffer, of
+// the reference's backward (src/attention.h:84-90 through src/softmax.h:13-36,
+// src/masking.h:13-29, src/matmul.h:39-79).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.h"
+
+namespace dg {
+namespace sm100 {
+
+constexpr int kAttnBwdThreads = 192;
+
+struct AttnBwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq_acc;
+  bf16* dk;
+  bf16* dv;
+  int64_t B, H, S;
+  int64_t row, bs;        // token stride / batch stride (elements) of dq_acc, dk, dv
+  float scale, scale_log2;
+  int causal;
+  int* status;
+};
+
+template <int DK>
+struct AttnBwdSmem {
+  static constexpr int kStages = DK == 64 ? 2 : 1;
+  static constexpr int kTileBytes = 128 * DK * 2;
+  static constexpr int kPBytes = 128 * 128 * 2;
+  static constexpr int kTotal = kTileBytes * (2 + 2 * kStages) + 2 * kPBytes + 512 + 1024;
+};
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]
+template <int DK>
+__global__ void __launch_bounds__(256) attn_delta_kernel(float* __restrict__ delta, const bf16* __restrict__ o,
+                                                         const bf16* __restrict__ d_o, int64_t B, int64_t H, int64_t S,
+                                                         int64_t row, int64_t bs) {
+  const int64_t total = B * S * H;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t h = i % H, s = (i / H) % S, b = i / (H * S);
+    const bf16* po = o + b * bs + s * row + h * DK;
+    const bf16* pd = d_o + b * bs + s * row + h * DK;
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < DK / 8; ++q) {
+      Vec16<bf16> a, g;
+      a.load(po + q * 8); g.load(pd + q * 8);
+      float fa[8], fg[8];
+      a.unpack(fa); g.unpack(fg);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += fa[e] * fg[e];
+    }
+    delta[(b * H + h) * S + s] = acc;
+  }
+}
+
+template <int DK>
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const AttnBwdParams p) {
+  using SM = AttnBwdSmem<DK>;
+  constexpr int STG = SM::kStages;
+  constexpr int NCH = DK / 64;
+  constexpr bool kAlias = (DK == 128);              // dQ shares the S columns: strictly ordered instead of overlapped
+  constexpr uint32_t kIdescSdP = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t kIdescAcc = make_idesc_bf16(128, DK, 1, 1);   // A = P / dS as MN-major, B = dO / Q MN-major
+  constexpr uint32_t kIdescDQ = make_idesc_bf16(128, DK, 0, 1);    // A = dS K-major, B = K MN-major
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t cS = 0, cDP = 128, cDV = 256, cDK = 256 + DK, cDQ = kAlias ? 0 : 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + SM::kTileBytes;
+  uint8_t* sQ = sV + SM::kTileBytes;                 // [STG]
+  uint8_t* sDO = sQ + STG * SM::kTileBytes;          // [STG]
+  uint8_t* sP = sDO + STG * SM::kTileBytes;
+  uint8_t* sDS = sP + SM::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + SM::kPBytes);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = kv_full + 1;        // [STG]
+  uint64_t* qdo_empty = qdo_full + STG;    // [STG]
+  uint64_t* sdp_full = qdo_empty + STG;
+  uint64_t* s_free = sdp_full + 1;
+  uint64_t* pds_ready = s_free + 1;
+  uint64_t* pds_free = pds_ready + 1;
+  uint64_t* dq_full = pds_free + 1;
+  uint64_t* dq_free = dq_full + 1;
+  uint64_t* acc_full = dq_free + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int key0 = jt * 128;
+  const int q_tiles = (int)((p.S + 127) / 128);
+  const int i0 = p.causal ? jt : 0;
+  const int N = q_tiles - i0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < STG; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(s_free, 4); mbar_init(pds_ready, 128); mbar_init(pds_free, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, 4); mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(kv_full, 2 * SM::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        tma_load_4d(sK + c * 16384, &tmK, kv_full, c * 64, key0, h, b);
+        tma_load_4d(sV + c * 16384, &tmV, kv_full, c * 64, key0, h, b);
+      }
+      int stage = 0; uint32_t phase = 0;
+      for (int n = 0; n < N && ok; ++n) {
+        ok = bounded_wait(&qdo_empty[stage], phase ^ 1u, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&qdo_full[stage], 2 * SM::kTileBytes);
+        const int q0 = (i0 + n) * 128;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tma_load_4d(sQ + stage * SM::kTileBytes + c * 16384, &tmQ, &qdo_full[stage], c * 64, q0, h, b);
+          tma_load_4d(sDO + stage * SM::kTileBytes + c * 16384, &tmDO, &qdo_full[stage], c * 64, q0, h, b);
+        }
+        if (++stage == STG) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) { if (p.status) atomicExch(p.status, 0x21); *abort_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = bounded_wait(kv_full, 0, abort_flag);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
+      auto issue_sdp = [&](int n) -> bool {
+        const int st = n % STG;
+        if (!bounded_wait(&qdo_full[st], (n / STG) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * SM::kTileBytes), aDO = smem_u32(sDO + st * SM::kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_f16(tmem_base + cS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), kIdescSdP,
+                   ks > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_f16(tmem_base + cDP, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), kIdescSdP,
+                   ks > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int n = 0; n < N && ok; ++n) {
+        const int st = n % STG;
+        if (!kAlias && n + 1 < N) {
+          ok = bounded_wait(s_free, n & 1, abort_flag) && issue_sdp(n + 1);
+          if (!ok) break;
+        }
+        ok = bounded_wait(pds_ready, n & 1, abort_flag);
+        if (ok && n > 0 && !kAlias) ok = bounded_wait(dq_free, (n - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * SM::kTileBytes), aDO = smem_u32(sDO + st * SM::kTileBytes);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {   // k = 16 query rows per step
+          umma_f16(tmem_base + cDV, make_smem_desc(aP + t * 2048, 16384, 1024), make_smem_desc(aDO + t * 2048, 16384, 1024),
+                   kIdescAcc, (n > 0 || t > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          umma_f16(tmem_base + cDK, make_smem_desc(aDS + t * 2048, 16384, 1024), make_smem_desc(aQ + t * 2048, 16384, 1024),
+                   kIdescAcc, (n > 0 || t > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {   // k = 16 keys per step
+          umma_f16(tmem_base + cDQ, make_smem_desc(aDS + (t / 4) * 16384 + (t % 4) * 32, 16, 1024),
+                   make_smem_desc(aK + t * 2048, 16384, 1024), kIdescDQ, t > 0 ? 1u : 0u);
+        }
+        umma_commit(dq_full);
+        umma_commit(&qdo_empty[st]);
+        umma_commit(pds_free);
+        if (kAlias && n + 1 < N) {
+          ok = bounded_wait(dq_free, n & 1, abort_flag) && issue_sdp(n + 1);
+          if (!ok) break;
+        }
+      }
+      if (ok) umma_commit(acc_full);
+      else { if (p.status) atomicExch(p.status, 0x22); *abort_flag = 1; }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax-gradient warps (2..5)
+    const int lg = warp & 3;
+    const int r = lg * 32 + lane;                       // row inside the current tile
+    const uint32_t lane_base = (uint32_t)(lg * 32) << 16;
+    const int sw = r & 7;
+    uint8_t* prow = sP + r * 128;
+    uint8_t* dsrow = sDS + r * 128;
+    bool ok = true;
+    for (int n = 0; n < N; ++n) {
+      const int it = i0 + n;
+      const int64_t qrow = (int64_t)it * 128 + r;
+      const bool row_ok = qrow < p.S;
+      float lse2 = 0.f, dlt = 0.f;
+      if (row_ok) {
+        const int64_t li = ((int64_t)b * p.H + h) * p.S + qrow;
+        lse2 = p.lse[li] * 1.4426950408889634f;
+        dlt = p.delta[li];
+      }
+      ok = bounded_wait(sdp_full, n & 1, abort_flag);
+      if (ok && n > 0) ok = bounded_wait(pds_free, (n - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool need_mask = (p.causal && it == jt) || (key0 + 128 > p.S);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_base + lane_base + cS + c * 32, rs);
+        tmem_ld_32x32(tmem_base + lane_base + cDP + c * 32, rp);
+        tc_wait_ld();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float pe = row_ok ? exp2f(__uint_as_float(rs[e]) * p.scale_log2 - lse2) : 0.f;
+          if (need_mask) {
+            const int64_t key = key0 + c * 32 + e;
+            if (key >= p.S || (p.causal && key > qrow)) pe = 0.f;
+          }
+          pv[e] = pe;
+          ds[e] = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
+        }
+        const int cb = (c >> 1) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 a, d;
+          __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
+          __nv_bfloat162* hd = reinterpret_cast<__nv_bfloat162*>(&d);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            ha[e] = __floats2bfloat162_rn(pv[q * 8 + 2 * e], pv[q * 8 + 2 * e + 1]);
+            hd[e] = __floats2bfloat162_rn(ds[q * 8 + 2 * e], ds[q * 8 + 2 * e + 1]);
+          }
+          const int q16 = (((c & 1) * 4 + q) ^ sw) << 4;
+          *reinterpret_cast<uint4*>(prow + cb + q16) = a;
+          *reinterpret_cast<uint4*>(dsrow + cb + q16) = d;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      // dQ_i partial: TMEM -> fp32 atomics
+      ok = bounded_wait(dq_full, n & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float* dq = p.dq_acc + (int64_t)b * p.bs + qrow * p.row + (int64_t)h * DK;
+#pragma unroll 1
+      for (int c = 0; c < DK / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(tmem_base + lane_base + cDQ + c * 32, raw);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) atomicAdd(dq + c * 32 + e, __uint_as_float(raw[e]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+    }
+    // dV_j, dK_j: TMEM -> bf16 global (row = key)
+    if (ok) {
+      ok = bounded_wait(acc_full, 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int64_t key = (int64_t)key0 + r;
+      bf16* dvrow = p.dv + (int64_t)b * p.bs + key * p.row + (int64_t)h * DK;
+      bf16* dkrow = p.dk + (int64_t)b * p.bs + key * p.row + (int64_t)h * DK;
+#pragma unroll 1
+      for (int c = 0; c < DK / 32; ++c) {
+        uint32_t rv[32], rk[32];
+        tmem_ld_32x32(tmem_base + lane_base + cDV + c * 32, rv);
+        tmem_ld_32x32(tmem_base + lane_base + cDK + c * 32, rk);
+        tc_wait_ld();
+        if (key < p.S) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 a, d;
+            __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
+            __nv_bfloat162* hd = reinterpret_cast<__nv_bfloat162*>(&d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              ha[e] = __floats2bfloat162_rn(__uint_as_float(rv[q * 8 + 2 * e]), __uint_as_float(rv[q * 8 + 2 * e + 1]));
+              hd[e] = __floats2bfloat162_rn(__uint_as_float(rk[q * 8 + 2 * e]), __uint_as_float(rk[q * 8 + 2 * e + 1]));
+            }
+            *reinterpret_cast<uint4*>(dvrow + c * 32 + q * 8) = a;
+            *reinterpret_cast<uint4*>(dkrow + c * 32 + q * 8) = d;
+          }
+        }
+      }
+    } else if (lane == 0) {
+      if (p.status) atomicExch(p.status, 0x23);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+template <int DK>
+int launch_attn_bwd(const dg_attn_bwd_args* a, cudaStream_t stream) {
+  using SM = AttnBwdSmem<DK>;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_tmap_bf16_4d(&tq, a->q, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
+  if (make_tmap_bf16_4d(&tk, a->k, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
+  if (make_tmap_bf16_4d(&tv, a->v, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
+  if (make_tmap_bf16_4d(&tdo, a->d_o, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
+  const int64_t rows = a->B * a->S * a->H;
+  attn_delta_kernel<DK><<<grid_for(rows, 256), 256, 0, stream>>>(a->delta, (const bf16*)a->o, (const bf16*)a->d_o, a->B,
+                                                                 a->H, a->S, a->row, a->bs);
+  DG_CHECK_LAUNCH();
+  cudaError_t me = cudaMemsetAsync(a->dq_acc, 0, sizeof(float) * (size_t)(a->B * a->bs), stream);
+  if (me != cudaSuccess) return (int)me;
+  AttnBwdParams p;
+  p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = (bf16*)a->dk_; p.dv = (bf16*)a->dv;
+  p.B = a->B; p.H = a->H; p.S = a->S; p.row = a->row; p.bs = a->bs;
+  p.scale = a->scale; p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.causal = a->causal; p.status = a->status;
+  auto kern = attn_bwd_kernel<DK>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((unsigned)((a->S + 127) / 128), (unsigned)a->H, (unsigned)a->B);
+  kern<<<grid, kAttnBwdThreads, SM::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  DG_CHECK_LAUNCH();
+  // dq (bf16) = dq_acc (fp32)
+  return dg_cast(DG_BF16, a->dq, DG_F32, a->dq_acc, a->B * a->bs, stream);
+}
+
+}  // namespace sm100
+}  // namespace dg
+
+extern "C" int dg_attention_bwd_sm100(const dg_attn_bwd_args* a, cudaStream_t stream) {
+  if (!a || !a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk_ || !a->dv || !a->delta ||
+      !a->dq_acc)
+    return DG_ERR_BAD_ARG;
+  if (a->B < 1 || a->H < 1 || a->S < 1 || a->B > 65535 || a->H > 65535) return DG_ERR_BAD_ARG;
+  if (a->row % 8 || a->bs % 8 || a->bs != a->S * a->row) return DG_ERR_UNSUPPORTED;
+  if (a->dk == 64) return dg::sm100::launch_attn_bwd<64>(a, stream);
+  if (a->dk == 128) return dg::sm100::launch_attn_bwd<128>(a, stream);
+  return DG_ERR_UNSUPPORTED;
+}

@@ -70,6 +70,50 @@ __global__ void __launch_bounds__(256) reduce_cols_partial_kernel(float* __restr
   }
 }
 
+// Vector form of stage 1: every thread owns VN adjacent columns (one 16-byte load per row).
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_partial_vec_kernel(float* __restrict__ partial,
+                                                                      const T* __restrict__ x,
+                                                                      const float* __restrict__ shift, int64_t R,
+                                                                      int64_t C, int64_t rows_per_split, int S,
+                                                                      int square) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float sh[8][32 * VN + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z, s = blockIdx.y;
+  const int64_t c0 = ((int64_t)blockIdx.x * 32 + tx) * VN;
+  const int64_t r0 = s * rows_per_split;
+  int64_t r1 = r0 + rows_per_split;
+  if (r1 > R) r1 = R;
+  float acc[VN];
+#pragma unroll
+  for (int k = 0; k < VN; ++k) acc[k] = 0.f;
+  if (c0 < C) {
+    float sv[VN];
+#pragma unroll
+    for (int k = 0; k < VN; ++k) sv[k] = shift ? shift[b * C + c0 + k] : 0.f;
+    const T* p = x + b * R * C + c0;
+    for (int64_t r = r0 + ty; r < r1; r += 8) {
+      Vec16<T> t; t.load(p + r * C);
+      float f[VN]; t.unpack(f);
+#pragma unroll
+      for (int k = 0; k < VN; ++k) { float v = f[k] - sv[k]; acc[k] += square ? v * v : v; }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VN; ++k) sh[ty][tx * VN + k] = acc[k];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * VN; i += blockDim.x) {
+    const int64_t c = (int64_t)blockIdx.x * 32 * VN + i;
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += sh[k][i];
+      partial[(b * S + s) * C + c] = t;
+    }
+  }
+}
+
 // Stage 2: fold the S partials. post: 0 -> scale*sum into T out; 1 -> sqrt(scale*sum); also optional fp32 copy.
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_cols_fold_kernel(T* __restrict__ out, float* __restrict__ out_f32,
@@ -111,7 +155,7 @@ __global__ void __launch_bounds__(256) sum_all_fold_kernel(T* __restrict__ out, 
 }
 
 static inline int cols_splits(int64_t B, int64_t R, int64_t C) {
-  int64_t col_blocks = (C + 31) / 32;
+  int64_t col_blocks = (C + 255) / 256;
   int64_t want = (148 * 4 + B * col_blocks - 1) / (B * col_blocks);
   int64_t max_s = (R + 63) / 64;
   if (want > max_s) want = max_s;
@@ -127,9 +171,15 @@ int launch_reduce_cols(void* out, void* mean_out, const void* x, int64_t B, int6
   const int64_t rps = (R + S - 1) / S;
   float* mean_f = (float*)scratch;
   float* partial = mean_f + B * C;
-  dim3 grid((unsigned)((C + 31) / 32), (unsigned)S, (unsigned)B);
+  constexpr int VN = Vec16<T>::N;
+  const bool vec = (C % VN == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+  dim3 grid((unsigned)(vec ? (C + 32 * VN - 1) / (32 * VN) : (C + 31) / 32), (unsigned)S, (unsigned)B);
   const int fold_blocks = grid_for(B * C, 256);
-  reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, nullptr, R, C, rps, S, 0);
+  auto stage1 = [&](const float* shift, int square) {
+    if (vec) reduce_cols_partial_vec_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, shift, R, C, rps, S, square);
+    else reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, shift, R, C, rps, S, square);
+  };
+  stage1(nullptr, 0);
   DG_CHECK_LAUNCH();
   if (mode == DG_RED_SUM || mode == DG_RED_MEAN) {
     float scale = mode == DG_RED_SUM ? 1.f : 1.f / (float)R;
@@ -140,7 +190,7 @@ int launch_reduce_cols(void* out, void* mean_out, const void* x, int64_t B, int6
   reduce_cols_fold_kernel<T><<<fold_blocks, 256, 0, stream>>>((T*)mean_out, mean_f, partial, B * C, C, S,
                                                               1.f / (float)R, 0);
   DG_CHECK_LAUNCH();
-  reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, mean_f, R, C, rps, S, 1);
+  stage1(mean_f, 1);
   DG_CHECK_LAUNCH();
   reduce_cols_fold_kernel<T><<<fold_blocks, 256, 0, stream>>>((T*)out, nullptr, partial, B * C, C, S,
                                                               1.f / (float)R, mode == DG_RED_STD ? 1 : 0);

@@ -43,4 +43,21 @@ inline int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner,
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+
+// bf16 4-D map {d0 (contiguous), d1, d2, d3} with element strides s1, s2, s3 and a
+// {box0, box1, 1, 1} box, 128-byte swizzle. Used for [B, S, H, dk] attention operands.
+inline int make_tmap_bf16_4d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                             uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box0, uint32_t box1) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -3;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
+  cuuint32_t box[4] = {box0, box1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 }  // namespace dg

@@ -1143,6 +1143,25 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = False, scale: floa
     return _result(od, lambda: AttentionBackward(qd, kd, vd, p, scale, causal), (q, k, v))
 
 
+class FlashAttentionBackward(Node):
+    """Backward of the fused tcgen05 attention: probabilities are recomputed from the saved
+    log-sum-exp, so nothing of size S x S is kept between forward and backward."""
+
+    def __init__(self, q, k, v, o, lse, H, causal, scale):
+        super().__init__()
+        self.saved = (q, k, v, o, lse)
+        self.H, self.causal, self.scale = H, causal, scale
+
+    def apply(self, grads):
+        q, k, v, o, lse = self.saved
+        g = _grad(grads, q.shape, q.dtype, q.device)
+        dq, dk, dv = K.attention_bwd(q, k, v, o, g, lse, self.H, self.causal, self.scale)
+        return [dq, dk, dv]
+
+    def release_variables(self):
+        self.saved = None
+
+
 class MhaCoreBackward(Node):
     def __init__(self, inner, B, S, H, dk):
         super().__init__()
@@ -1168,6 +1187,10 @@ def mha_core(q: Tensor, k: Tensor, v: Tensor, n_heads: int, causal: bool = False
     H = n_heads
     dk = D // H
     scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    if K.attention_supported(q.data, H) and q.dtype == k.dtype == v.dtype:
+        qd, kd, vd = _c(q), _c(k), _c(v)
+        od, lse = K.attention_fwd(qd, kd, vd, H, causal, scale)
+        return _result(od, lambda: FlashAttentionBackward(qd, kd, vd, od, lse, H, causal, scale), (q, k, v))
     split = lambda t: K.contiguous(_c(t).reshape(B, S, H, dk).transpose(1, 2))  # noqa: E731
     qd, kd, vd = split(q), split(k), split(v)
     s = K.gemm2d(qd, kd, trans_b=True)

@@ -504,6 +504,9 @@ def _gemm_status_word(device) -> torch.Tensor:
 _STATUS: dict = {}
 # "auto": tcgen05 for bf16 when the TMA rules hold, SIMT otherwise. "simt" forces the SIMT kernel.
 GEMM_BACKEND = "auto"
+# split-K for weight-gradient shapes (few output tiles, long K): on/off and the CTA count to aim for
+SPLIT_K = True
+SPLIT_K_TARGET_CTAS = 148
 
 
 def gemm_status(device=None) -> int:
@@ -570,6 +573,24 @@ def gemm2d(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, ou
     lib = L.load()
     use_tc = (GEMM_BACKEND == "auto" and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
               and out.dtype in (torch.bfloat16, torch.float32))
+    if (use_tc and SPLIT_K and trans_a and not trans_b and batch == 1 and bias is None and epi == 0
+            and a.is_contiguous() and b.is_contiguous()):
+        # weight-gradient shape: few output tiles, very long K. Split K over the batch dimension of
+        # the same kernel (fp32 partial products), then fold the partials in a fixed order.
+        tiles = ((M + 127) // 128) * ((N + 255) // 256 if N > 128 else 1)
+        s = min(SPLIT_K_TARGET_CTAS // max(tiles, 1), K // 1024)
+        while s > 1 and (K % s or (K // s) % 8):
+            s -= 1
+        if s > 1:
+            part = torch.empty(s, M, N, dtype=torch.float32, device=a.device)
+            gemm2d(a.view(s, K // s, M), b.view(s, K // s, N), trans_a=True, out_dtype=torch.float32, alpha=alpha,
+                   out=part)
+            folded, _ = reduce_cols(part.view(1, s, M * N), RED_SUM)
+            folded = folded.view(M, N)
+            if residual is not None:
+                folded = ew("ADD", folded, cast(residual, torch.float32), out=folded)
+            assign_(out, folded)
+            return out
     if use_tc:
         args = L.GemmArgs()
         args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
@@ -617,3 +638,49 @@ def gemm2d(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, ou
     if tmp is not out:
         assign_(out, tmp)
     return out
+
+
+# ----------------------------------------------------------------------------- fused attention
+def attention_supported(q: torch.Tensor, n_heads: int) -> bool:
+    """True when the tcgen05 attention kernels can take q/k/v of shape [B, S, H*dk] in place."""
+    if not q.is_cuda or q.dtype != torch.bfloat16 or q.dim() != 3:
+        return False
+    D = q.shape[-1]
+    return D % n_heads == 0 and (D // n_heads) in (64, 128) and L.has("dg_attention_fwd_sm100")
+
+
+def attention_fwd(q, k, v, n_heads: int, causal: bool, scale: float):
+    """q, k, v: [B, S, H*dk] bf16 contiguous. Returns (o [B, S, H*dk], lse [B, H, S] fp32)."""
+    B, S, D = q.shape
+    dk = D // n_heads
+    o = torch.empty_like(q)
+    lse = torch.empty(B, n_heads, S, dtype=torch.float32, device=q.device)
+    a = L.AttnFwdArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    a.B, a.H, a.S, a.dk = B, n_heads, S, dk
+    a.q_row = a.k_row = a.v_row = a.o_row = D
+    a.q_bs = a.k_bs = a.v_bs = a.o_bs = S * D
+    a.scale, a.causal = scale, 1 if causal else 0
+    a.status = _gemm_status_word(q.device).data_ptr()
+    L.check(L.load().dg_attention_fwd_sm100(C.byref(a), L.stream_ptr()), "dg_attention_fwd_sm100")
+    _cnt()
+    return o, lse
+
+
+def attention_bwd(q, k, v, o, d_o, lse, n_heads: int, causal: bool, scale: float):
+    """Gradients of attention_fwd. All tensors [B, S, H*dk] bf16 contiguous; lse [B, H, S] fp32."""
+    B, S, D = q.shape
+    dq, dk_, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    delta = torch.empty(B, n_heads, S, dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty(B, S, D, dtype=torch.float32, device=q.device)
+    a = L.AttnBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_o, a.lse = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                                        lse.data_ptr())
+    a.dq, a.dk_, a.dv, a.delta, a.dq_acc = dq.data_ptr(), dk_.data_ptr(), dv.data_ptr(), delta.data_ptr(), dq_acc.data_ptr()
+    a.B, a.H, a.S, a.dk = B, n_heads, S, D // n_heads
+    a.row, a.bs = D, S * D
+    a.scale, a.causal = scale, 1 if causal else 0
+    a.status = _gemm_status_word(q.device).data_ptr()
+    L.check(L.load().dg_attention_bwd_sm100(C.byref(a), L.stream_ptr()), "dg_attention_bwd_sm100")
+    _cnt(4)
+    return dq, dk_, dv
