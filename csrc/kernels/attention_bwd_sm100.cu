@@ -7,8 +7,8 @@
 //     dV_j += P^T dO_i                dK_j += dS^T Q_i                dQ_i += dS K_j
 // Five MMAs per (i, j). The same shared-memory tiles serve as K-major and as MN-major operands
 // (a 128-byte-swizzled [rows][64] tile can be read either way through the UMMA descriptor), so
-// nothing is transposed. dQ partial tiles are added to an fp32 [B, S, H*dk] accumulator with
-// red.global.add.f32 and converted once at the end; Delta_i = rowsum(dO_i * O_i) comes from a
+// nothing is transposed. dQ partial tiles are added to an fp32 [B, S, H*dk] accumulator with a
+// TMA reduce-add from shared memory and converted once at the end; Delta_i = rowsum(dO_i * O_i) comes from a
 // small pre-pass. Replaces the five separate ops, each with its own S x S gradient buffer, of
 // the reference's backward (src/attention.h:84-90 through src/softmax.h:13-36,
 // src/masking.h:13-29, src/matmul.h:39-79).
@@ -19,7 +19,7 @@
 namespace dg {
 namespace sm100 {
 
-constexpr int kAttnBwdThreads = 192;
+constexpr int kAttnBwdThreads = 320;   // TMA warp, MMA warp, 8 gradient warps (two per TMEM lane group)
 
 struct AttnBwdParams {
   const float* lse;
@@ -39,7 +39,8 @@ struct AttnBwdSmem {
   static constexpr int kStages = DK == 64 ? 2 : 1;
   static constexpr int kTileBytes = 128 * DK * 2;
   static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kTotal = kTileBytes * (2 + 2 * kStages) + 2 * kPBytes + 512 + 1024;
+  static constexpr int kDQBytes = 2 * 128 * 128;       // two [128 rows x 32 fp32] slabs for the dQ reduce-add
+  static constexpr int kTotal = kTileBytes * (2 + 2 * kStages) + 2 * kPBytes + kDQBytes + 512 + 1024;
 };
 
 // delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]
@@ -66,11 +67,17 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(float* __restrict__ del
   }
 }
 
+__device__ __forceinline__ float ex2_approx_b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int DK>
 __global__ void __launch_bounds__(kAttnBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
   using SM = AttnBwdSmem<DK>;
   constexpr int STG = SM::kStages;
   constexpr int NCH = DK / 64;
@@ -89,7 +96,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sDO = sQ + STG * SM::kTileBytes;          // [STG]
   uint8_t* sP = sDO + STG * SM::kTileBytes;
   uint8_t* sDS = sP + SM::kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + SM::kPBytes);
+  uint8_t* sDQ = sDS + SM::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDQ + SM::kDQBytes);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = kv_full + 1;        // [STG]
   uint64_t* qdo_empty = qdo_full + STG;    // [STG]
@@ -113,8 +121,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < STG; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(s_free, 4); mbar_init(pds_ready, 128); mbar_init(pds_free, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_free, 4); mbar_init(acc_full, 1);
+    mbar_init(sdp_full, 1); mbar_init(s_free, 8); mbar_init(pds_ready, 256); mbar_init(pds_free, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, 8); mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
@@ -214,8 +222,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       else { if (p.status) atomicExch(p.status, 0x22); *abort_flag = 1; }
     }
   } else {
-    // ------------------------------------------------------------------ softmax-gradient warps (2..5)
+    // ------------------------------------------------------------------ softmax-gradient warps (2..9)
+    // Two warps share each TMEM lane group (= 32 query rows); they split the columns in halves.
+    // Nothing is reduced along a row here (LSE and Delta are precomputed), so the split is free.
     const int lg = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = lg * 32 + lane;                       // row inside the current tile
     const uint32_t lane_base = (uint32_t)(lg * 32) << 16;
     const int sw = r & 7;
@@ -239,7 +250,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const bool need_mask = (p.causal && it == jt) || (key0 + 128 > p.S);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tmem_base + lane_base + cS + c * 32, rs);
         tmem_ld_32x32(tmem_base + lane_base + cDP + c * 32, rp);
@@ -247,7 +258,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float pv[32], ds[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float pe = row_ok ? exp2f(__uint_as_float(rs[e]) * p.scale_log2 - lse2) : 0.f;
+          float pe = row_ok ? ex2_approx_b(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2)) : 0.f;
           if (need_mask) {
             const int64_t key = key0 + c * 32 + e;
             if (key >= p.S || (p.causal && key > qrow)) pe = 0.f;
@@ -281,15 +292,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float* dq = p.dq_acc + (int64_t)b * p.bs + qrow * p.row + (int64_t)h * DK;
+      // Each half-warp-group packs one [128 x 32] fp32 slab (128-byte swizzle) per round; one thread
+      // then hands both slabs to the TMA unit, which adds them into the fp32 accumulator in full
+      // 128-byte lines (scalar atomics from registers would be 8192 four-byte transactions per tile).
+      const bool issuer = (threadIdx.x == 64);
 #pragma unroll 1
-      for (int c = 0; c < DK / 32; ++c) {
+      for (int rd = 0; rd < DK / 64; ++rd) {
+        const int c = half * (DK / 64) + rd;
         uint32_t raw[32];
         tmem_ld_32x32(tmem_base + lane_base + cDQ + c * 32, raw);
         tc_wait_ld();
-        if (row_ok) {
+        if (issuer) bulk_wait_read0();            // the previous round's reduce has read its slabs
+        named_bar_sync(1, 256);
+        uint8_t* srow = sDQ + half * 16384 + r * 128;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) atomicAdd(dq + c * 32 + e, __uint_as_float(raw[e]));
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(srow + ((q ^ sw) << 4)) = make_uint4(raw[q * 4], raw[q * 4 + 1], raw[q * 4 + 2], raw[q * 4 + 3]);
+        fence_proxy_async_smem();
+        named_bar_sync(2, 256);
+        if (issuer) {
+          tma_reduce_add_4d(&tmDQ, sDQ, rd * 32, it * 128, h, b);
+          tma_reduce_add_4d(&tmDQ, sDQ + 16384, (DK / 64 + rd) * 32, it * 128, h, b);
+          bulk_commit();
         }
       }
       tc_fence_before();
@@ -307,7 +331,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bf16* dvrow = p.dv + (int64_t)b * p.bs + key * p.row + (int64_t)h * DK;
       bf16* dkrow = p.dk + (int64_t)b * p.bs + key * p.row + (int64_t)h * DK;
 #pragma unroll 1
-      for (int c = 0; c < DK / 32; ++c) {
+      for (int c = half * (DK / 64); c < (half + 1) * (DK / 64); ++c) {
         uint32_t rv[32], rk[32];
         tmem_ld_32x32(tmem_base + lane_base + cDV + c * 32, rv);
         tmem_ld_32x32(tmem_base + lane_base + cDK + c * 32, rk);
@@ -332,6 +356,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (p.status) atomicExch(p.status, 0x23);
       *abort_flag = 1;
     }
+    if (threadIdx.x == 64) bulk_wait_all();       // reduce-adds must have left shared memory
   }
 
   tc_fence_before();
@@ -347,6 +372,8 @@ int launch_attn_bwd(const dg_attn_bwd_args* a, cudaStream_t stream) {
   if (make_tmap_bf16_4d(&tk, a->k, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
   if (make_tmap_bf16_4d(&tv, a->v, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
   if (make_tmap_bf16_4d(&tdo, a->d_o, DK, a->S, a->H, a->B, a->row, DK, a->bs, 64, 128)) return DG_ERR_DRIVER;
+  CUtensorMap tdq;
+  if (make_tmap_f32_4d(&tdq, a->dq_acc, DK, a->S, a->H, a->B, a->row, DK, a->bs, 128)) return DG_ERR_DRIVER;
   const int64_t rows = a->B * a->S * a->H;
   attn_delta_kernel<DK><<<grid_for(rows, 256), 256, 0, stream>>>(a->delta, (const bf16*)a->o, (const bf16*)a->d_o, a->B,
                                                                  a->H, a->S, a->row, a->bs);
@@ -366,7 +393,7 @@ int launch_attn_bwd(const dg_attn_bwd_args* a, cudaStream_t stream) {
     attr_set = true;
   }
   dim3 grid((unsigned)((a->S + 127) / 128), (unsigned)a->H, (unsigned)a->B);
-  kern<<<grid, kAttnBwdThreads, SM::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, kAttnBwdThreads, SM::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
   DG_CHECK_LAUNCH();
   // dq (bf16) = dq_acc (fp32)
   return dg_cast(DG_BF16, a->dq, DG_F32, a->dq_acc, a->B * a->bs, stream);

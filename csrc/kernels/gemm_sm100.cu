@@ -3,6 +3,7 @@
 #include <unordered_map>
 #include <string>
 #include <cstring>
+#include <cstdlib>
 #include "gemm_sm100.cuh"
 #include "tma_host.h"
 
@@ -12,9 +13,11 @@ namespace sm100 {
 template <int BN, int STAGES, bool A_K, bool B_K, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux,
                          const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_cta_body<BN, STAGES, A_K, B_K, OutT, false, false>(&tmA, &tmB, p, smem_raw, (int)blockIdx.x, (int)gridDim.x);
+  gemm_cta_body<BN, STAGES, A_K, B_K, OutT, false, false>(&tmA, &tmB, &tmD, &tmAux, p, smem_raw, (int)blockIdx.x,
+                                                          (int)gridDim.x);
 }
 
 struct TmapKey {
@@ -79,10 +82,49 @@ void fill_params(GemmParams* p, const dg_gemm_args* a) {
   p->a_bcast = (a->a_bs == 0);
   p->b_bcast = (a->b_bs == 0);
   p->bias_bs = a->bias_bs;
+  static int dbg = -1;
+  if (dbg < 0) { const char* e = getenv("DG_GEMM_DEBUG"); dbg = e ? atoi(e) : 0; }
+  p->debug = dbg;
+}
+
+// Output (and saved pre-activation) maps for the staged TMA-store epilogue; sets p->tma_store / tma_aux.
+void build_output_maps(CUtensorMap* tmD, CUtensorMap* tmAux, GemmParams* p, const dg_gemm_args* a) {
+  std::memset(tmD, 0, sizeof(*tmD));
+  std::memset(tmAux, 0, sizeof(*tmAux));
+  p->tma_store = p->tma_aux = 0;
+  const int esize = a->out_dtype == DG_F32 ? 4 : 2;
+  const int64_t batch = a->batch < 1 ? 1 : a->batch;
+  auto ok = [&](const void* ptr, int es) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && (a->ldd * es) % 16 == 0 &&
+           (batch == 1 || (a->d_bs * es) % 16 == 0);
+  };
+  if (!ok(a->D, esize)) return;
+  const bool saves_pre = a->aux && (a->epi == DG_EPI_GELU || a->epi == DG_EPI_RELU);
+  if (saves_pre && !(esize == 2 && ok(a->aux, 2))) {
+    // pre-activation cannot take the staged path: keep everything on direct stores
+    if (esize == 2) return;
+  }
+  TmapKey k{{(uint64_t)(uintptr_t)a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)batch, (uint64_t)a->ldd,
+             (uint64_t)a->d_bs, (uint64_t)(0x100 + esize), 32}};
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    auto it = g_tmap_cache.find(k);
+    if (it != g_tmap_cache.end()) *tmD = it->second;
+    else {
+      if (make_tmap_out_3d(tmD, esize, a->D, a->N, a->M, batch, a->ldd, a->d_bs, 128 / esize, 32)) return;
+      g_tmap_cache.emplace(k, *tmD);
+    }
+  }
+  p->tma_store = 1;
+  if (saves_pre && esize == 2) {
+    if (make_tmap_out_3d(tmAux, 2, a->aux, a->N, a->M, batch, a->ldd, a->d_bs, 64, 32)) { p->tma_store = 0; return; }
+    p->tma_aux = 1;
+  }
 }
 
 template <int BN, int STAGES, bool A_K, bool B_K, typename OutT>
-int launch_plain(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+int launch_plain(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmAux,
+                 const GemmParams& p, cudaStream_t stream) {
   using SM = GemmSmem<BN, STAGES>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_K, B_K, OutT>;
   static bool attr_set = false;
@@ -94,19 +136,19 @@ int launch_plain(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParam
   const int64_t m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
   int64_t tiles = m_tiles * n_tiles * p.batch;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, kGemmThreads, SM::kTotal, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, SM::kTotal, stream>>>(tmA, tmB, tmD, tmAux, p);
   DG_CHECK_LAUNCH();
   return DG_OK;
 }
 
 template <int BN, int STAGES>
-int dispatch_layout(const dg_gemm_args* a, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                    cudaStream_t s) {
+int dispatch_layout(const dg_gemm_args* a, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
+                    const CUtensorMap& tmAux, const GemmParams& p, cudaStream_t s) {
   const bool ak = a->a_kmajor != 0, bk = a->b_kmajor != 0, f32 = a->out_dtype == DG_F32;
 #define DG_L(AK, BK)                                                                          \
   if (ak == AK && bk == BK)                                                                   \
-    return f32 ? launch_plain<BN, STAGES, AK, BK, float>(tmA, tmB, p, s)                      \
-               : launch_plain<BN, STAGES, AK, BK, bf16>(tmA, tmB, p, s);
+    return f32 ? launch_plain<BN, STAGES, AK, BK, float>(tmA, tmB, tmD, tmAux, p, s)          \
+               : launch_plain<BN, STAGES, AK, BK, bf16>(tmA, tmB, tmD, tmAux, p, s);
   DG_L(true, true) DG_L(true, false) DG_L(false, true) DG_L(false, false)
 #undef DG_L
   return DG_ERR_BAD_ARG;
@@ -140,8 +182,11 @@ extern "C" int dg_gemm_sm100(const dg_gemm_args* a, cudaStream_t stream) {
   if (rc) return rc;
   GemmParams p;
   fill_params(&p, a);
-  if (BN == 256) return dispatch_layout<256, 4>(a, tmA, tmB, p, stream);
-  return dispatch_layout<128, 6>(a, tmA, tmB, p, stream);
+  CUtensorMap tmD, tmAux;
+  build_output_maps(&tmD, &tmAux, &p, a);
+  if (p.debug & 16) p.tma_store = p.tma_aux = 0;   // timing experiments: direct global stores
+  if (BN == 256) return dispatch_layout<256, 4>(a, tmA, tmB, tmD, tmAux, p, stream);
+  return dispatch_layout<128, 6>(a, tmA, tmB, tmD, tmAux, p, stream);
 }
 
 extern "C" int dg_version(void) { return 100; }

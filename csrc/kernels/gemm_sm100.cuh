@@ -7,7 +7,7 @@
 //                           STAGES-deep shared-memory ring, mbarrier complete_tx signalling
 //   warp 1   MMA issuer   : one thread issues tcgen05.mma (M=128, N=BN, K=16) x4 per 64-wide
 //                           k block, tcgen05.commit releases the smem stage / publishes the tile
-//   warps 2-5 epilogue    : tcgen05.ld of the fp32 accumulator (double-buffered in TMEM so the
+//   warps 2-9 epilogue    : tcgen05.ld of the fp32 accumulator (double-buffered in TMEM so the
 //                           next tile's main loop overlaps), bias / GELU / dGELU / residual,
 //                           16-byte global stores
 // Operand layouts are chosen per call through the UMMA descriptors (K-major or MN-major for
@@ -27,7 +27,7 @@ namespace sm100 {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane group)
 constexpr int kGroupM = 8;
 
 struct GemmParams {
@@ -41,6 +41,9 @@ struct GemmParams {
   float alpha;
   int* status;
   int a_bcast, b_bcast;      // operand shared by every batch entry (its tensor map has batch extent 1)
+  int tma_store;             // epilogue output goes through shared memory + TMA store (alignment rules met)
+  int tma_aux;               // the saved pre-activation goes the same way (needs bf16 output)
+  int debug;                 // bit 0: epilogue drops its results (timing experiments only)
   int64_t bias_bs;           // element stride of the bias between batch entries (0: shared)
   // ---- fused-collective hooks (unused by the plain GEMM) ----
   // all-gather -> GEMM: rows [c*rows_per_chunk, ...) of A may be loaded once a_flags[c] >= a_epoch
@@ -62,7 +65,8 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kOutStageBytes = 8 * 4096;   // one [32 x 128 B] slab per epilogue warp
+  static constexpr int kTotal = STAGES * kStageBytes + kOutStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void decode_tile(int64_t t, int64_t m_tiles, int64_t n_tiles, int64_t& b, int64_t& mt,
@@ -94,7 +98,8 @@ template <> struct OutVec<bf16> {
         *reinterpret_cast<uint4*>(dst + q * 8) = pk;
       }
     } else {
-      for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) if (e < valid) dst[e] = __float2bfloat16_rn(v[e]);
     }
   }
   static __device__ __forceinline__ void load(const bf16* src, float* v, bool vec_ok, int valid) {
@@ -110,6 +115,7 @@ template <> struct OutVec<bf16> {
         }
       }
     } else {
+#pragma unroll
       for (int e = 0; e < 32; ++e) v[e] = e < valid ? __bfloat162float(src[e]) : 0.f;
     }
   }
@@ -121,7 +127,8 @@ template <> struct OutVec<float> {
       for (int q = 0; q < 8; ++q)
         *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
     } else {
-      for (int e = 0; e < valid; ++e) dst[e] = v[e];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) if (e < valid) dst[e] = v[e];
     }
   }
   static __device__ __forceinline__ void load(const float* src, float* v, bool vec_ok, int valid) {
@@ -132,10 +139,28 @@ template <> struct OutVec<float> {
         v[q * 4] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
       }
     } else {
+#pragma unroll
       for (int e = 0; e < 32; ++e) v[e] = e < valid ? src[e] : 0.f;
     }
   }
 };
+
+// tanh-approximation GELU on the hardware tanh (one MUFU op); used where the result is rounded
+// to bf16 anyway.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanh_fast(u));
+}
+__device__ __forceinline__ float gelu_grad_fast(float x) {
+  const float x2 = x * x;
+  const float t = tanh_fast(0.7978845608f * (x + 0.044715f * x * x2));
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * (0.7978845608f * (1.f + 0.134145f * x2));
+}
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -165,8 +190,9 @@ __device__ __forceinline__ bool bounded_flag_wait(const int* flag, int epoch, vo
 // The GEMM roles of one CTA. `cta_rank`/`cta_count` give this CTA's slot among the CTAs that
 // run the GEMM role (fused kernels reserve other CTAs of the grid for copy/reduce roles).
 template <int BN, int STAGES, bool A_KMAJOR, bool B_KMAJOR, typename OutT, bool GATE_A, bool SCATTER_D>
-__device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p,
-                                              uint8_t* smem_raw, int cta_rank, int cta_count) {
+__device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD,
+                                              const CUtensorMap* tmAux, const GemmParams& p, uint8_t* smem_raw,
+                                              int cta_rank, int cta_count) {
   using SM = GemmSmem<BN, STAGES>;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two >= 32");
@@ -175,7 +201,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
   // 1024-byte aligned carve-up (128-byte swizzle atoms are 1024 bytes)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * SM::kStageBytes);
+  uint8_t* out_stage = smem + STAGES * SM::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + SM::kOutStageBytes);
   uint64_t* full_bar = bars;                      // [STAGES]
   uint64_t* empty_bar = bars + STAGES;            // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;        // [2]
@@ -188,7 +215,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
     *abort_flag = 0;
     *never_flag = 0;
     fence_barrier_init();
@@ -269,11 +296,17 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase_bits = 0;   // bit a: phase of accumulator buffer a
       int acc = 0;
       bool ok = true;
+      // The issuing thread is on the critical path of every k block: keep its instruction count small.
+      constexpr uint32_t kStepA = A_KMAJOR ? 32u : 2048u, kStepB = B_KMAJOR ? 32u : 2048u;
+      const uint32_t s0 = smem_u32(tiles);
+      const uint64_t desc_a0 = A_KMAJOR ? make_smem_desc(s0, 16, 1024) : make_smem_desc(s0, 8192, 1024);
+      const uint64_t desc_b0 = B_KMAJOR ? make_smem_desc(s0 + SM::kABytes, 16, 1024)
+                                        : make_smem_desc(s0 + SM::kABytes, 8192, 1024);
       for (int64_t t = cta_rank; t < total_tiles && ok; t += cta_count) {
-        ok = bounded_wait(&tempty_bar[acc], acc_phase[acc] ^ 1u, abort_flag);
+        ok = bounded_wait(&tempty_bar[acc], ((acc_phase_bits >> acc) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
@@ -281,23 +314,20 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
           ok = bounded_wait(&full_bar[stage], phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(tiles + stage * SM::kStageBytes);
-          const uint32_t sb = sa + SM::kABytes;
+          // descriptors differ from the stage-0 / k-0 ones only in the 14-bit start-address field
+          const uint64_t da0 = desc_a0 + (uint64_t)((uint32_t)(stage * SM::kStageBytes) >> 4);
+          const uint64_t db0 = desc_b0 + (uint64_t)((uint32_t)(stage * SM::kStageBytes) >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            uint64_t da, db;
-            if constexpr (A_KMAJOR) da = make_smem_desc(sa + k * 32, 16, 1024);
-            else da = make_smem_desc(sa + k * 2048, 8192, 1024);
-            if constexpr (B_KMAJOR) db = make_smem_desc(sb + k * 32, 16, 1024);
-            else db = make_smem_desc(sb + k * 2048, 8192, 1024);
-            umma_f16(tmem_d, da, db, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(tmem_d, da0 + (uint64_t)(k * (kStepA >> 4)), db0 + (uint64_t)(k * (kStepB >> 4)), kIdesc,
+                     (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // smem stage reusable once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&tfull_bar[acc]);      // accumulator complete
-        acc_phase[acc] ^= 1u;
+        acc_phase_bits ^= (1u << acc);
         acc ^= 1;
       }
       if (!ok) {
@@ -306,9 +336,11 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each TMEM lane group (32 output rows) and take one half of the tile's columns.
     const int lane_group = warp & 3;  // TMEM sub-partition this warp may read
-    uint32_t acc_phase[2] = {0, 0};
+    const int half = (warp - 2) >> 2;
+    uint32_t acc_phase_bits = 0;   // bit a: phase of accumulator buffer a
     int acc = 0;
     bool ok = true;
     const bool d_vec_base = ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) && ((p.ldd * sizeof(OutT)) % 16 == 0) &&
@@ -317,7 +349,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
       int64_t b, mt, nt;
       decode_tile(t, m_tiles, n_tiles, b, mt, nt);
       if constexpr (GATE_A) mt = (mt + p.m_tile_rotate) % m_tiles;
-      ok = bounded_wait(&tfull_bar[acc], acc_phase[acc], abort_flag);
+      ok = bounded_wait(&tfull_bar[acc], (acc_phase_bits >> acc) & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -333,69 +365,145 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
       }
       const bf16* auxrow = p.aux ? reinterpret_cast<const bf16*>(p.aux) + b * p.d_bs + row * p.ldd : nullptr;
       const OutT* resrow = p.residual ? reinterpret_cast<const OutT*>(p.residual) + b * p.d_bs + row * p.ldd : nullptr;
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        const int64_t col0 = nt * BN + ch * 32;
-        uint32_t raw[32];
-        const uint32_t taddr = tmem_base + (uint32_t)(acc * BN + ch * 32) + ((uint32_t)(lane_group * 32) << 16);
-        tmem_ld_32x32(taddr, raw);
-        tc_wait_ld();
-        if (ch == BN / 32 - 1) {
-          // accumulator fully read: hand the TMEM buffer back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        }
-        if (col0 >= p.N || !row_ok) continue;
-        int valid = (int)((p.N - col0) < 32 ? (p.N - col0) : 32);
-        const bool vec_ok = d_vec_base && valid == 32;
-        float v[32];
+      const int ch_begin = half * (BN / 64), ch_end = (half + 1) * (BN / 64);
+      // Values of one 32-column chunk of this thread's row. `pre_only` stops after alpha and bias
+      // (the pre-activation that the GELU / ReLU epilogues also save).
+      auto chunk_values = [&](const uint32_t (&raw)[32], float (&v)[32], int64_t col0, int valid, bool vec_in,
+                              bool pre_only, bool aux_direct) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
         if (p.bias) {
           if (p.bias_dtype == DG_BF16) {
             const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + b * p.bias_bs + col0;
+            if (valid == 32 && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0) {
+              float bv[32];
+              OutVec<bf16>::load(bp, bv, true, 32);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += __bfloat162float(bp[e]);
+              for (int e = 0; e < 32; ++e) v[e] += bv[e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (e < valid) v[e] += __bfloat162float(bp[e]);
+            }
           } else {
             const float* bp = reinterpret_cast<const float*>(p.bias) + b * p.bias_bs + col0;
 #pragma unroll
             for (int e = 0; e < 32; ++e) if (e < valid) v[e] += bp[e];
           }
         }
+        if (pre_only) return;
         if (p.epi == DG_EPI_GELU || p.epi == DG_EPI_RELU) {
-          if (p.aux) OutVec<bf16>::store(reinterpret_cast<bf16*>(p.aux) + b * p.d_bs + row * p.ldd + col0, v,
-                                         vec_ok && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
+          if (p.aux && aux_direct && row_ok)
+            OutVec<bf16>::store(reinterpret_cast<bf16*>(p.aux) + b * p.d_bs + row * p.ldd + col0, v,
+                                vec_in && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
           if (p.epi == DG_EPI_GELU) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = gelu_f(v[e]);
+            for (int e = 0; e < 32; ++e) v[e] = gelu_fast(v[e]);
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = v[e] > 0.f ? v[e] : 0.f;
           }
-        } else if (p.epi == DG_EPI_DGELU || p.epi == DG_EPI_DRELU) {
+        } else if ((p.epi == DG_EPI_DGELU || p.epi == DG_EPI_DRELU) && row_ok) {
           float a[32];
-          OutVec<bf16>::load(auxrow + col0, a, vec_ok && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
+          OutVec<bf16>::load(auxrow + col0, a, vec_in && ((reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0), valid);
           if (p.epi == DG_EPI_DGELU) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] *= gelu_grad_f(a[e]);
+            for (int e = 0; e < 32; ++e) v[e] *= gelu_grad_fast(a[e]);
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = a[e] > 0.f ? v[e] : 0.f;
           }
         }
-        if (resrow) {
+        if (resrow && row_ok) {
           float r[32];
-          OutVec<OutT>::load(resrow + col0, r, vec_ok && ((reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0), valid);
+          OutVec<OutT>::load(resrow + col0, r, vec_in && ((reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0), valid);
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] += r[e];
         }
-        OutVec<OutT>::store(drow + col0, v, vec_ok, valid);
+      };
+      auto release_tmem = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      };
+
+      bool use_tma = false;
+      if constexpr (!SCATTER_D) use_tma = p.tma_store != 0;
+      if (use_tma) {
+        // ---- staged path: each warp packs a [32 rows x 128 bytes] slab in shared memory (128-byte
+        // swizzle) and one thread hands it to the TMA store unit; full 128-byte lines reach L2 and
+        // edge tiles are clipped by the tensor map.
+        constexpr int kCh = sizeof(OutT) == 2 ? 2 : 1;   // 32-column chunks per slab row
+        uint8_t* slab = out_stage + (warp - 2) * 4096;
+        uint8_t* slab_row = slab + lane * 128;
+        const int sw = lane & 7;
+        const bool two_pass = p.tma_aux != 0;            // GELU / ReLU with a saved pre-activation (bf16)
+        const int npass = two_pass ? 2 : 1;
+        const int row0_warp = (int)(mt * kBM + lane_group * 32);
+#pragma unroll 1
+        for (int s0 = ch_begin; s0 < ch_end; s0 += kCh) {
+          const int64_t col_slab = nt * BN + s0 * 32;
+#pragma unroll 1
+          for (int pass = 0; pass < npass; ++pass) {
+            const bool aux_pass = two_pass && pass == 0;
+            if (lane == 0) bulk_wait_read0();            // previous store has finished reading the slab
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < kCh; ++k) {
+              const int ch = s0 + k;
+              const int64_t col0 = nt * BN + ch * 32;
+              uint32_t raw[32];
+              tmem_ld_32x32(tmem_base + (uint32_t)(acc * BN + ch * 32) + ((uint32_t)(lane_group * 32) << 16), raw);
+              tc_wait_ld();
+              if (ch == ch_end - 1 && pass == npass - 1) release_tmem();
+              if (col0 >= p.N || (p.debug & 1)) continue;
+              const int valid = (int)((p.N - col0) < 32 ? (p.N - col0) : 32);
+              float v[32];
+              chunk_values(raw, v, col0, valid, d_vec_base && valid == 32, aux_pass, !two_pass);
+              if (p.debug & 8) { if (v[0] == 123.456f) slab_row[0] = 1; continue; }
+              if (sizeof(OutT) == 2 || aux_pass) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 pk;
+                  __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1]);
+                  *reinterpret_cast<uint4*>(slab_row + (((k * 4 + q) ^ sw) << 4)) = pk;
+                }
+              } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  *reinterpret_cast<float4*>(slab_row + ((q ^ sw) << 4)) =
+                      make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              }
+            }
+            if (!(p.debug & 4)) fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && col_slab < p.N && !(p.debug & 3)) {
+              tma_store_3d(aux_pass ? tmAux : tmD, slab, (int)col_slab, row0_warp, (int)b);
+              bulk_commit();
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int ch = ch_begin; ch < ch_end; ++ch) {
+          const int64_t col0 = nt * BN + ch * 32;
+          uint32_t raw[32];
+          tmem_ld_32x32(tmem_base + (uint32_t)(acc * BN + ch * 32) + ((uint32_t)(lane_group * 32) << 16), raw);
+          tc_wait_ld();
+          if (ch == ch_end - 1) release_tmem();
+          if (col0 >= p.N || !row_ok) continue;
+          const int valid = (int)((p.N - col0) < 32 ? (p.N - col0) : 32);
+          const bool vec_ok = d_vec_base && valid == 32;
+          float v[32];
+          chunk_values(raw, v, col0, valid, vec_ok, false, true);
+          OutVec<OutT>::store(drow + col0, v, vec_ok, valid);
+        }
       }
       if constexpr (SCATTER_D) {
         // publish the tile to its destination: all four epilogue warps have stored their rows
         __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (warp == 2 && lane == 0) {
           const int64_t dest = (mt * kBM) / p.rows_per_dest;
           const int64_t tiles_per_dest = (p.rows_per_dest / kBM) * n_tiles;
@@ -403,9 +511,10 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
           st_release_sys(p.dest_flags[dest] + (int64_t)p.src_rank * tiles_per_dest + ltile, p.d_epoch);
         }
       }
-      acc_phase[acc] ^= 1u;
+      acc_phase_bits ^= (1u << acc);
       acc ^= 1;
     }
+    if (lane == 0) bulk_wait_all();   // outstanding TMA stores must leave shared memory before the CTA exits
     if (!ok && lane == 0) {
       if (p.status) atomicExch(p.status, 3);
       *abort_flag = 1;

@@ -1,0 +1,200 @@
+// Second half of the engine: device helpers, gradient accumulation, leaf sinks and the
+// topological backward sweep (reference: src/engine.h:265-399). Included by engine.h users
+// through dummy.h; kept separate so engine.h stays a readable statement of the data model.
+#pragma once
+#include "engine.h"
+
+namespace dgshim {
+
+using TP = std::shared_ptr<Tensor>;
+
+inline TP make(const std::vector<int>& shape, bool req_grad = false) { return std::make_shared<Tensor>(shape, req_grad); }
+
+inline int64_t numel(const std::vector<int>& shape) {
+  int64_t n = 1;
+  for (int d : shape) n *= d;
+  return n;
+}
+
+// last two dims as (batch, r, c); 1-D tensors are rows of one
+inline void brc(const std::vector<int>& shape, int64_t& B, int64_t& r, int64_t& c) {
+  c = shape.back();
+  r = shape.size() >= 2 ? shape[shape.size() - 2] : 1;
+  B = numel(shape) / (r * c);
+}
+
+// Stride-aware gather into a fresh contiguous tensor (device side).
+inline TP contiguous(const TP& t) {
+  if (t->is_contiguous()) return t;
+  auto out = make(t->shape, false);
+  std::vector<int64_t> sh(t->shape.begin(), t->shape.end()), ss(t->strides.begin(), t->strides.end());
+  auto ds_i = make_strides(t->shape);
+  std::vector<int64_t> ds(ds_i.begin(), ds_i.end());
+  check(dg_strided_copy(0, out->dev_rw(), ds.data(), t->dev_ro(), ss.data(), sh.data(), (int)sh.size(), stream()),
+        "strided copy");
+  return out;
+}
+
+// out = op(x, y, z, w) over out's shape; operands must be contiguous.
+inline TP ew(int op, const std::vector<int>& shape, const TP& x, const TP& y = nullptr, const TP& z = nullptr,
+             const TP& w = nullptr, int ymode = BC_SAME, int zmode = BC_SAME, int wmode = BC_SAME, float s0 = 0.f,
+             float s1 = 0.f) {
+  auto out = make(shape, false);
+  int64_t B, r, c;
+  brc(shape, B, r, c);
+  check(dg_elementwise(op, 0, out->dev_rw(), x ? x->dev_ro() : nullptr, y ? y->dev_ro() : nullptr,
+                       z ? z->dev_ro() : nullptr, w ? w->dev_ro() : nullptr, ymode, zmode, wmode, s0, s1, B * r * c, r, c,
+                       stream()),
+        "elementwise kernel");
+  return out;
+}
+
+inline TP clone(const TP& t) { auto c = contiguous(t); return ew(EW_COPY, c->shape, c); }
+
+// x [R, C] -> [R] reduced over the last dim; result gets `out_shape`
+inline TP reduce_rows(const TP& x, int64_t R, int64_t C, int mode, const std::vector<int>& out_shape, TP* mean = nullptr) {
+  auto out = make(out_shape, false);
+  if (mean) *mean = make(out_shape, false);
+  check(dg_reduce_rows(0, out->dev_rw(), mean ? (*mean)->dev_rw() : nullptr, x->dev_ro(), R, C, mode, stream()),
+        "row reduction");
+  return out;
+}
+
+// x [B, R, C] -> [B, C] reduced over R
+inline TP reduce_cols(const TP& x, int64_t B, int64_t R, int64_t C, int mode, const std::vector<int>& out_shape,
+                      TP* mean = nullptr) {
+  auto out = make(out_shape, false);
+  auto mean_t = make(out_shape, false);
+  DevBuf scratch((size_t)std::max<int64_t>(dg_reduce_cols_scratch_bytes(B, R, C), 4));
+  check(dg_reduce_cols(0, out->dev_rw(), mean_t->dev_rw(), x->dev_ro(), B, R, C, mode, scratch.p, stream()),
+        "column reduction");
+  if (mean) *mean = mean_t;
+  return out;
+}
+
+inline TP sum_all(const TP& x, float scale, const std::vector<int>& out_shape) {
+  auto out = make(out_shape, false);
+  DevBuf scratch(1024 * sizeof(float));
+  check(dg_sum_all(0, out->dev_rw(), x->dev_ro(), x->size(), scale, scratch.p, stream()), "full reduction");
+  return out;
+}
+
+}  // namespace dgshim
+
+// Identity when contiguous, else a gather copy; no autograd node (reference: src/engine.h:265-275)
+inline std::shared_ptr<Tensor> make_contiguous(const std::shared_ptr<Tensor>& t) {
+  auto c = dgshim::contiguous(t);
+  if (c != t) c->requires_grad = t->requires_grad;
+  return c;
+}
+
+inline std::shared_ptr<Tensor> Tensor::_reshape(const std::vector<int>& new_shape) {
+  if (dgshim::numel(new_shape) != size()) throw std::runtime_error("reshape: element count differs");
+  auto c = dgshim::contiguous(shared_from_this());
+  auto v = c->alias(new_shape, make_strides(new_shape));
+  v->requires_grad = requires_grad;
+  return v;
+}
+
+// dst += src honouring strides; clones src when dst is null (reference: src/engine.h:280-295)
+inline void tensor_add_inplace(std::shared_ptr<Tensor>& dst, const std::shared_ptr<Tensor>& src) {
+  if (!dst) { dst = dgshim::clone(src); return; }
+  auto s = dgshim::contiguous(src);
+  if (dst->is_contiguous()) {
+    dgshim::check(dg_accumulate(0, dst->dev_rw(), s->dev_ro(), dst->size(), dgshim::stream()), "accumulate");
+  } else {
+    auto sum = dgshim::ew(dgshim::EW_ADD, dst->shape, dgshim::contiguous(dst), s);
+    std::vector<int64_t> sh(dst->shape.begin(), dst->shape.end()), ds(dst->strides.begin(), dst->strides.end());
+    auto ss_i = make_strides(dst->shape);
+    std::vector<int64_t> ss(ss_i.begin(), ss_i.end());
+    dgshim::check(dg_strided_copy(0, dst->dev_rw(), ds.data(), sum->dev_ro(), ss.data(), sh.data(), (int)sh.size(),
+                                  dgshim::stream()), "strided copy");
+  }
+}
+
+// Leaf sink: var->grad += g (reference: src/engine.h:298-312)
+struct AccumulateGrad : Node {
+  std::weak_ptr<Tensor> variable;
+  explicit AccumulateGrad(const std::shared_ptr<Tensor>& v) : variable(v) {}
+  std::vector<std::shared_ptr<Tensor>> apply(const std::vector<std::shared_ptr<Tensor>>& grads) override {
+    auto var = variable.lock();
+    if (var && !grads.empty() && grads[0]) {
+      auto g = grads[0];
+      if (g->shape != var->shape) g = dgshim::contiguous(g)->alias(var->shape, make_strides(var->shape));
+      tensor_add_inplace(var->grad, g);
+      if (var->grad) var->grad->requires_grad = false;
+    }
+    return {};
+  }
+};
+
+// Null edge when no grad is needed, else grad_fn, else the lazily created accumulator
+// (reference: src/engine.h:315-322)
+inline Edge get_grad_edge(const std::shared_ptr<Tensor>& t) {
+  if (!t->requires_grad) return Edge(nullptr, 0);
+  if (t->grad_fn) return Edge(t->grad_fn, 0);
+  if (!t->grad_accumulator) t->grad_accumulator = std::make_shared<AccumulateGrad>(t);
+  return Edge(t->grad_accumulator, 0);
+}
+
+// Reverse sweep from a one-element root in topological (Kahn) order (reference: src/engine.h:325-399).
+// Gradients are values: a gradient that reaches a node from two consumers is summed into a buffer
+// the engine owns, never into one of the contributions.
+inline void Tensor::backward(bool retain_graph) {
+  if (size() != 1) throw std::runtime_error("backward() can only be called on a scalar tensor");
+  grad_ptr()[0] = 1.0f;
+  if (!grad_fn) return;
+  std::unordered_map<Node*, int> indeg;
+  std::vector<Node*> stack{grad_fn.get()};
+  indeg[grad_fn.get()] = 0;
+  while (!stack.empty()) {           // iterative: graph depth is not bounded by the C++ stack
+    Node* n = stack.back();
+    stack.pop_back();
+    for (auto& e : n->next_edges) {
+      if (!e.function) continue;
+      auto it = indeg.find(e.function.get());
+      if (it == indeg.end()) { indeg[e.function.get()] = 1; stack.push_back(e.function.get()); }
+      else it->second++;
+    }
+  }
+  struct Slot { std::shared_ptr<Tensor> g; bool owned = false; };
+  std::unordered_map<Node*, Slot> slots;
+  std::queue<std::shared_ptr<Node>> ready;
+  auto seed = dgshim::make(shape, false);
+  dgshim::check(dg_fill(0, seed->dev_rw(), seed->size(), 1.0f, dgshim::stream()), "fill");
+  slots[grad_fn.get()] = Slot{seed, true};
+  ready.push(grad_fn);
+  while (!ready.empty()) {
+    auto node = ready.front();
+    ready.pop();
+    std::vector<std::shared_ptr<Tensor>> outs;
+    auto sit = slots.find(node.get());
+    std::shared_ptr<Tensor> incoming;
+    if (sit != slots.end() && sit->second.g) { incoming = sit->second.g; outs = node->apply({incoming}); slots.erase(sit); }
+    for (size_t i = 0; i < node->next_edges.size(); ++i) {
+      auto& fn = node->next_edges[i].function;
+      if (!fn) continue;
+      std::shared_ptr<Tensor> og = i < outs.size() ? outs[i] : nullptr;
+      if (og) {
+        auto& slot = slots[fn.get()];
+        if (!slot.g) {
+          int uses = 0;
+          for (auto& o : outs) if (o == og) ++uses;
+          slot.g = og;
+          slot.owned = (og != incoming) && uses == 1 && og.use_count() <= 2 + 0 && og->is_contiguous();
+        } else {
+          if (slot.owned) {
+            tensor_add_inplace(slot.g, og);
+          } else {
+            auto a = dgshim::contiguous(slot.g), b = dgshim::contiguous(og);
+            if (b->shape != a->shape) b = b->alias(a->shape, make_strides(a->shape));
+            slot.g = dgshim::ew(dgshim::EW_ADD, a->shape, a, b);
+            slot.owned = true;
+          }
+        }
+      }
+      if (--indeg[fn.get()] == 0) ready.push(fn);
+    }
+    if (!retain_graph) { node->next_edges.clear(); node->release_variables(); }
+  }
+}

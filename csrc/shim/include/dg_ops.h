@@ -1,0 +1,220 @@
+// The reference's differentiable free functions and backward-node types, on device kernels.
+// Names, argument conventions and numerical definitions follow src/ops.h, src/scalar_ops.h,
+// src/broadcasting.h, src/matmul.h, src/transpose.h, src/view.h, src/concat.h, src/cool_ops.h,
+// src/masking.h, src/softmax.h, src/sum.h, src/mean.h, src/var.h, src/std.h, src/loss.h and
+// src/activations.h of the reference; every op is correct for strided inputs and gradients are
+// values (never aliases of the incoming gradient that are later accumulated into).
+#pragma once
+#include "dg_engine_impl.h"
+
+namespace dgshim {
+
+using Grads = std::vector<TP>;
+
+template <class NodeT, class... Args>
+inline void attach(const TP& out, const std::vector<TP>& inputs, Args&&... args) {
+  bool need = false;
+  for (auto& t : inputs) need = need || t->requires_grad;
+  out->requires_grad = need;
+  if (!need) return;
+  auto node = std::make_shared<NodeT>(std::forward<Args>(args)...);
+  for (size_t i = 0; i < inputs.size(); ++i) node->add_next_edge(get_grad_edge(inputs[i]).function, (int)i);
+  out->grad_fn = node;
+}
+
+inline TP gin(const Grads& g, const std::vector<int>& shape) {
+  auto c = contiguous(g[0]);
+  if (c->shape != shape) c = c->alias(shape, make_strides(shape));
+  return c;
+}
+
+inline void same_shape(const TP& a, const TP& b, const char* what) {
+  if (a->shape != b->shape) throw std::runtime_error(std::string(what) + ": shapes differ");
+}
+
+}  // namespace dgshim
+
+// ------------------------------------------------------------------ binary ops (src/ops.h)
+struct AddBackward : Node {
+  dgshim::Grads apply(const dgshim::Grads& g) override { return {g[0], g[0]}; }  // engine never mutates shared grads
+};
+inline std::shared_ptr<Tensor> add(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b) {
+  using namespace dgshim;
+  same_shape(a, b, "add");
+  auto out = ew(EW_ADD, a->shape, contiguous(a), contiguous(b));
+  attach<AddBackward>(out, {a, b});
+  return out;
+}
+
+struct SubBackward : Node {
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    auto gc = dgshim::contiguous(g[0]);
+    return {gc, dgshim::ew(dgshim::EW_NEG, gc->shape, gc)};
+  }
+};
+inline std::shared_ptr<Tensor> sub(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b) {
+  using namespace dgshim;
+  same_shape(a, b, "sub");
+  auto out = ew(EW_SUB, a->shape, contiguous(a), contiguous(b));
+  attach<SubBackward>(out, {a, b});
+  return out;
+}
+
+struct MulBackward : Node {
+  dgshim::TP a, b;
+  MulBackward(dgshim::TP a_, dgshim::TP b_) : a(std::move(a_)), b(std::move(b_)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, a->shape);
+    return {ew(EW_MUL, a->shape, gc, b), ew(EW_MUL, a->shape, gc, a)};
+  }
+  void release_variables() override { a = b = nullptr; }
+};
+inline std::shared_ptr<Tensor> mul(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b) {
+  using namespace dgshim;
+  same_shape(a, b, "mul");
+  auto ac = contiguous(a), bc = contiguous(b);
+  auto out = ew(EW_MUL, a->shape, ac, bc);
+  attach<MulBackward>(out, {a, b}, ac, bc);
+  return out;
+}
+
+struct DivBackward : Node {
+  dgshim::TP a, b;
+  DivBackward(dgshim::TP a_, dgshim::TP b_) : a(std::move(a_)), b(std::move(b_)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, a->shape);
+    return {ew(EW_DIV, a->shape, gc, b), ew(EW_DIV_BWD_B, a->shape, gc, b, a)};
+  }
+  void release_variables() override { a = b = nullptr; }
+};
+inline std::shared_ptr<Tensor> div(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b) {
+  using namespace dgshim;
+  same_shape(a, b, "div");
+  auto ac = contiguous(a), bc = contiguous(b);
+  auto out = ew(EW_DIV, a->shape, ac, bc);
+  attach<DivBackward>(out, {a, b}, ac, bc);
+  return out;
+}
+
+// Unary op with one saved tensor and a backward opcode: out' = bwd_op(g, saved; s0)
+struct UnaryBackwardBase : Node {
+  dgshim::TP saved;
+  int bwd_op;
+  float s0;
+  UnaryBackwardBase(dgshim::TP s, int op, float s0_) : saved(std::move(s)), bwd_op(op), s0(s0_) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    return {ew(bwd_op, saved->shape, gin(g, saved->shape), saved, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, s0)};
+  }
+  void release_variables() override {}
+};
+#define DG_UNARY_NODE(Name) \
+  struct Name : UnaryBackwardBase { using UnaryBackwardBase::UnaryBackwardBase; }
+DG_UNARY_NODE(PowBackward);
+DG_UNARY_NODE(SqrtBackward);
+DG_UNARY_NODE(LogBackward);
+DG_UNARY_NODE(ExpBackward);
+DG_UNARY_NODE(ReluBackward);
+DG_UNARY_NODE(TanhBackward);
+DG_UNARY_NODE(GeluBackward);
+DG_UNARY_NODE(RdivScalarBackward);
+DG_UNARY_NODE(BoolMaskBackward);
+
+namespace dgshim {
+// forward opcode fwd(x; s0); saves the input (save_out=false) or the output for the backward opcode
+template <class NodeT>
+inline TP unary(const TP& a, int fwd, int bwd, float s0 = 0.f, bool save_out = false, float bwd_s0 = 0.f) {
+  auto ac = contiguous(a);
+  auto out = ew(fwd, a->shape, ac, nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, s0);
+  attach<NodeT>(out, {a}, save_out ? out->alias(out->shape, out->strides) : ac, bwd, bwd_s0);  // alias: no node<->tensor cycle
+  return out;
+}
+}  // namespace dgshim
+
+inline std::shared_ptr<Tensor> pow(const std::shared_ptr<Tensor>& a, int n) {
+  return dgshim::unary<PowBackward>(a, dgshim::EW_POW_I, dgshim::EW_POW_BWD, (float)n, false, (float)n);
+}
+inline std::shared_ptr<Tensor> sqrt(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<SqrtBackward>(a, dgshim::EW_SQRT, dgshim::EW_SQRT_BWD);
+}
+// log(a + 1e-8), as the reference defines it (src/ops.h:295-297)
+inline std::shared_ptr<Tensor> log(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<LogBackward>(a, dgshim::EW_LOG_EPS, dgshim::EW_LOG_BWD, 1e-8f, false, 1e-8f);
+}
+inline std::shared_ptr<Tensor> exp(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<ExpBackward>(a, dgshim::EW_EXP, dgshim::EW_MUL, 0.f, true);
+}
+inline std::shared_ptr<Tensor> relu(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<ReluBackward>(a, dgshim::EW_RELU, dgshim::EW_RELU_BWD);
+}
+inline std::shared_ptr<Tensor> tanh(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<TanhBackward>(a, dgshim::EW_TANH, dgshim::EW_TANH_BWD, 0.f, true);
+}
+inline std::shared_ptr<Tensor> gelu(const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<GeluBackward>(a, dgshim::EW_GELU, dgshim::EW_GELU_BWD);
+}
+inline std::shared_ptr<Tensor> rdiv_scalar(float s, const std::shared_ptr<Tensor>& a) {
+  return dgshim::unary<RdivScalarBackward>(a, dgshim::EW_RDIV_S, dgshim::EW_RDIV_BWD, s, false, s);
+}
+
+// Sum of all elements -> [1, 1] (src/ops.h:350-385)
+struct SimpleSumBackward : Node {
+  std::vector<int> shape;
+  explicit SimpleSumBackward(std::vector<int> s) : shape(std::move(s)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    return {ew(EW_COPY_Y, shape, nullptr, contiguous(g[0]), nullptr, nullptr, BC_SCALAR)};
+  }
+};
+inline std::shared_ptr<Tensor> simple_sum(const std::shared_ptr<Tensor>& a) {
+  using namespace dgshim;
+  auto out = sum_all(contiguous(a), 1.0f, {1, 1});
+  attach<SimpleSumBackward>(out, {a}, a->shape);
+  return out;
+}
+
+// ------------------------------------------------------------------ scalar ops (src/scalar_ops.h)
+struct ScaleBackwardBase : Node {
+  float factor;
+  explicit ScaleBackwardBase(float f) : factor(f) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    if (factor == 1.0f) return {g[0]};
+    auto gc = contiguous(g[0]);
+    return {ew(EW_MUL_S, gc->shape, gc, nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, factor)};
+  }
+};
+#define DG_SCALE_NODE(Name) \
+  struct Name : ScaleBackwardBase { using ScaleBackwardBase::ScaleBackwardBase; }
+DG_SCALE_NODE(AddScalarBackward);
+DG_SCALE_NODE(SubScalarBackward);
+DG_SCALE_NODE(MulScalarBackward);
+DG_SCALE_NODE(DivScalarBackward);
+DG_SCALE_NODE(RsubScalarBackward);
+
+namespace dgshim {
+template <class NodeT>
+inline TP scalar_op(const TP& a, int op, float s, float grad_factor) {
+  auto out = ew(op, a->shape, contiguous(a), nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, s);
+  attach<NodeT>(out, {a}, grad_factor);
+  return out;
+}
+}  // namespace dgshim
+inline std::shared_ptr<Tensor> add_scalar(const std::shared_ptr<Tensor>& a, float s) {
+  return dgshim::scalar_op<AddScalarBackward>(a, dgshim::EW_ADD_S, s, 1.0f);
+}
+inline std::shared_ptr<Tensor> sub_scalar(const std::shared_ptr<Tensor>& a, float s) {
+  return dgshim::scalar_op<SubScalarBackward>(a, dgshim::EW_ADD_S, -s, 1.0f);
+}
+inline std::shared_ptr<Tensor> mul_scalar(const std::shared_ptr<Tensor>& a, float s) {
+  return dgshim::scalar_op<MulScalarBackward>(a, dgshim::EW_MUL_S, s, s);
+}
+inline std::shared_ptr<Tensor> div_scalar(const std::shared_ptr<Tensor>& a, float s) {
+  return dgshim::scalar_op<DivScalarBackward>(a, dgshim::EW_DIV_S, s, 1.0f / s);
+}
+inline std::shared_ptr<Tensor> neg(const std::shared_ptr<Tensor>& a) { return mul_scalar(a, -1.0f); }
+inline std::shared_ptr<Tensor> rsub_scalar(float s, const std::shared_ptr<Tensor>& a) {
+  return dgshim::scalar_op<RsubScalarBackward>(a, dgshim::EW_RSUB_S, s, -1.0f);
+}

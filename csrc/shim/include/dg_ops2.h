@@ -1,0 +1,222 @@
+// Second half of the op set: broadcasting, matmul, views, concat, masks, softmax, reductions,
+// losses (reference: src/broadcasting.h, src/matmul.h, src/transpose.h, src/view.h,
+// src/concat.h, src/cool_ops.h, src/masking.h, src/softmax.h, src/sum.h, src/mean.h, src/var.h,
+// src/std.h, src/loss.h).
+#pragma once
+#include "dg_ops.h"
+
+// ------------------------------------------------------------------ broadcast (src/broadcasting.h:5-84)
+struct BroadcastBackward : Node {
+  std::vector<int> in_shape, out_shape;
+  bool rows;
+  BroadcastBackward(std::vector<int> i, std::vector<int> o, bool r) : in_shape(std::move(i)), out_shape(std::move(o)), rows(r) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, out_shape);
+    int64_t B, r, c;
+    brc(out_shape, B, r, c);
+    return {rows ? reduce_cols(gc, B, r, c, RED_SUM, in_shape) : reduce_rows(gc, B * r, c, RED_SUM, in_shape)};
+  }
+};
+// Repeat the size-1 second-to-last dim (axis 0) or last dim (otherwise) n times.
+inline std::shared_ptr<Tensor> broadcast(const std::shared_ptr<Tensor>& a, int axis, int n) {
+  using namespace dgshim;
+  if (a->ndim() < 2) throw std::runtime_error("broadcast: needs at least 2 dims");
+  const int dim = axis == 0 ? a->ndim() - 2 : a->ndim() - 1;
+  if (a->shape[dim] != 1) throw std::runtime_error("broadcast: the broadcast dim must have size 1");
+  auto out_shape = a->shape;
+  out_shape[dim] = n;
+  auto out = ew(EW_COPY_Y, out_shape, nullptr, contiguous(a), nullptr, nullptr, axis == 0 ? BC_COLS : BC_ROWS);
+  attach<BroadcastBackward>(out, {a}, a->shape, out_shape, axis == 0);
+  return out;
+}
+
+// ------------------------------------------------------------------ cast_n_* (src/broadcasting.h:87-401)
+namespace dgshim {
+inline int cast_mode(const TP& x, const TP& y, const char* what) {
+  if (x->ndim() < 2) throw std::runtime_error(std::string(what) + ": x needs at least 2 dims");
+  const int r = x->shape[x->ndim() - 2], c = x->shape[x->ndim() - 1];
+  if (y->ndim() == x->ndim() && y->ndim() > 2) {
+    bool same_batch = true;
+    int64_t bprod = 1;
+    for (int i = 0; i < x->ndim() - 2; ++i) { same_batch = same_batch && x->shape[i] == y->shape[i]; bprod *= x->shape[i]; }
+    if (same_batch && bprod > 1) {
+      // keepdim statistic of x itself: broadcast per batch entry (the intended reading; the
+      // reference indexes batch 0's values for every entry, src/broadcasting.h:133-149)
+      const int yr = y->shape[y->ndim() - 2], yc = y->shape[y->ndim() - 1];
+      if (yc == 1 && yr == r) return BC_ROWS;
+      if (yr == 1 && yc == c) return BC_COLS;
+      if (yr == r && yc == c) return BC_SAME;
+      throw std::runtime_error(std::string(what) + ": y does not broadcast against x");
+    }
+  }
+  const int yr = y->ndim() > 1 ? y->shape[y->ndim() - 2] : 1, yc = y->shape[y->ndim() - 1];
+  if ((int64_t)yr * yc != numel(y->shape)) throw std::runtime_error(std::string(what) + ": y must be 2-D");
+  if ((yr != 1 && yr != r) || (yc != 1 && yc != c)) throw std::runtime_error(std::string(what) + ": y does not broadcast against x");
+  if (yr == r && yc == c) return BC_MAT;
+  if (yr == 1 && yc == c) return BC_ROW;
+  if (yr == r && yc == 1) return BC_COL;
+  return BC_SCALAR;
+}
+// Sum a full-shape gradient over the batch and over y's size-1 dims.
+inline TP reduce_to_y(const TP& full, int mode, const std::vector<int>& yshape) {
+  int64_t B, r, c;
+  brc(full->shape, B, r, c);
+  switch (mode) {
+    case BC_ROW: return reduce_cols(full, 1, B * r, c, RED_SUM, yshape);
+    case BC_COL: {
+      auto rows = reduce_rows(full, B * r, c, RED_SUM, {(int)(B * r)});
+      return reduce_cols(rows, 1, B, r, RED_SUM, yshape);
+    }
+    case BC_MAT: return reduce_cols(full, 1, B, r * c, RED_SUM, yshape);
+    case BC_ROWS: return reduce_rows(full, B * r, c, RED_SUM, yshape);
+    case BC_COLS: return reduce_cols(full, B, r, c, RED_SUM, yshape);
+    case BC_SAME: return full;
+    default: return sum_all(full, 1.0f, yshape);
+  }
+}
+}  // namespace dgshim
+
+struct CastBackwardBase : Node {
+  dgshim::TP x, y;
+  int mode, kind;  // kind: 0 add, 1 sub, 2 mul, 3 div
+  std::vector<int> xshape, yshape;
+  CastBackwardBase(dgshim::TP x_, dgshim::TP y_, int m, int k, std::vector<int> xs, std::vector<int> ys)
+      : x(std::move(x_)), y(std::move(y_)), mode(m), kind(k), xshape(std::move(xs)), yshape(std::move(ys)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, xshape);
+    if (kind == 0) return {gc, reduce_to_y(gc, mode, yshape)};
+    if (kind == 1) return {gc, reduce_to_y(ew(EW_NEG, xshape, gc), mode, yshape)};
+    if (kind == 2) return {ew(EW_MUL, xshape, gc, y, nullptr, nullptr, mode), reduce_to_y(ew(EW_MUL, xshape, gc, x), mode, yshape)};
+    return {ew(EW_DIV, xshape, gc, y, nullptr, nullptr, mode),
+            reduce_to_y(ew(EW_DIV_BWD_B, xshape, gc, y, x, nullptr, mode), mode, yshape)};
+  }
+  void release_variables() override { x = y = nullptr; }
+};
+struct CastAddBackward : CastBackwardBase { using CastBackwardBase::CastBackwardBase; };
+struct CastSubBackward : CastBackwardBase { using CastBackwardBase::CastBackwardBase; };
+struct CastMulBackward : CastBackwardBase { using CastBackwardBase::CastBackwardBase; };
+struct CastDivBackward : CastBackwardBase { using CastBackwardBase::CastBackwardBase; };
+
+namespace dgshim {
+template <class NodeT>
+inline TP cast_n(const TP& x, const TP& y, int op, int kind, const char* what) {
+  const int mode = cast_mode(x, y, what);
+  auto xc = contiguous(x), yc = contiguous(y);
+  auto out = ew(op, x->shape, xc, yc, nullptr, nullptr, mode);
+  attach<NodeT>(out, {x, y}, kind >= 2 ? xc : nullptr, kind >= 2 ? yc : nullptr, mode, kind, x->shape, y->shape);
+  return out;
+}
+}  // namespace dgshim
+inline std::shared_ptr<Tensor> cast_n_add(const std::shared_ptr<Tensor>& x, const std::shared_ptr<Tensor>& y) {
+  return dgshim::cast_n<CastAddBackward>(x, y, dgshim::EW_ADD, 0, "cast_n_add");
+}
+inline std::shared_ptr<Tensor> cast_n_sub(const std::shared_ptr<Tensor>& x, const std::shared_ptr<Tensor>& y) {
+  return dgshim::cast_n<CastSubBackward>(x, y, dgshim::EW_SUB, 1, "cast_n_sub");
+}
+inline std::shared_ptr<Tensor> cast_n_mul(const std::shared_ptr<Tensor>& x, const std::shared_ptr<Tensor>& y) {
+  return dgshim::cast_n<CastMulBackward>(x, y, dgshim::EW_MUL, 2, "cast_n_mul");
+}
+inline std::shared_ptr<Tensor> cast_n_div(const std::shared_ptr<Tensor>& x, const std::shared_ptr<Tensor>& y) {
+  return dgshim::cast_n<CastDivBackward>(x, y, dgshim::EW_DIV, 3, "cast_n_div");
+}
+
+// ------------------------------------------------------------------ matmul (src/matmul.h:86-200)
+namespace dgshim {
+// C[b] = op(A[b]) op(B[b]) on contiguous fp32 operands; a_bs / b_bs of 0 share the operand.
+inline TP gemm(const TP& a, const TP& b, int64_t batch, int64_t M, int64_t N, int64_t K, bool ta, bool tb, int64_t a_bs,
+               int64_t b_bs, const std::vector<int>& out_shape) {
+  auto out = make(out_shape, false);
+  const int64_t ars = ta ? 1 : K, acs = ta ? M : 1, brs = tb ? 1 : N, bcs = tb ? K : 1;
+  check(dg_gemm_simt(0, out->dev_rw(), a->dev_ro(), b->dev_ro(), batch, M, N, K, a_bs, ars, acs, b_bs, brs, bcs, M * N, N,
+                     1.0f, 0.0f, stream()), "matmul kernel");
+  return out;
+}
+// Materialise an operand over the broadcast batch shape (stride-0 expansion), or return it as is.
+inline bool all_ones(const std::vector<int>& v) {
+  for (int d : v) if (d != 1) return false;
+  return true;
+}
+inline TP expand_batch(const TP& t, const std::vector<int>& padded, const std::vector<int>& out_batch) {
+  if (padded == out_batch || all_ones(padded)) return contiguous(t);   // an un-batched operand is shared (stride 0)
+  auto c = contiguous(t);
+  const int r = c->shape[c->ndim() - 2], cc = c->shape[c->ndim() - 1];
+  std::vector<int> shape = out_batch, strides;
+  shape.push_back(r); shape.push_back(cc);
+  auto pstr = make_strides([&] { auto s = padded; s.push_back(r); s.push_back(cc); return s; }());
+  for (size_t i = 0; i < out_batch.size(); ++i) strides.push_back(padded[i] == 1 ? 0 : pstr[i]);
+  strides.push_back(cc); strides.push_back(1);
+  auto view = c->alias(shape, strides);
+  return contiguous(view);
+}
+// Sum a [out_batch, r, c] gradient down to an operand with `padded` batch dims.
+inline TP sum_to_batch(const TP& full, const std::vector<int>& padded, const std::vector<int>& out_batch,
+                       const std::vector<int>& orig_shape) {
+  if (padded == out_batch) return full->alias(orig_shape, make_strides(orig_shape));
+  const int nb = (int)out_batch.size();
+  const int r = full->shape[nb], c = full->shape[nb + 1];
+  std::vector<int> red, keep;
+  for (int i = 0; i < nb; ++i) (padded[i] == 1 && out_batch[i] != 1 ? red : keep).push_back(i);
+  // permute reduced dims to the front
+  std::vector<int> pshape, pstrides;
+  for (int i : red) { pshape.push_back(full->shape[i]); pstrides.push_back(full->strides[i]); }
+  for (int i : keep) { pshape.push_back(full->shape[i]); pstrides.push_back(full->strides[i]); }
+  pshape.push_back(r); pshape.push_back(c);
+  pstrides.push_back(full->strides[nb]); pstrides.push_back(full->strides[nb + 1]);
+  auto moved = contiguous(full->alias(pshape, pstrides));
+  int64_t R = 1, rest = (int64_t)r * c;
+  for (int i : red) R *= out_batch[i];
+  for (int i : keep) rest *= out_batch[i];
+  return reduce_cols(moved, 1, R, rest, RED_SUM, orig_shape);
+}
+}  // namespace dgshim
+
+struct MatmulBackward : Node {
+  dgshim::TP a, b;   // contiguous, expanded to the broadcast batch
+  std::vector<int> pa, pb, out_batch, ashape, bshape;
+  MatmulBackward(dgshim::TP a_, dgshim::TP b_, std::vector<int> pa_, std::vector<int> pb_, std::vector<int> ob,
+                 std::vector<int> as, std::vector<int> bs)
+      : a(std::move(a_)), b(std::move(b_)), pa(std::move(pa_)), pb(std::move(pb_)), out_batch(std::move(ob)),
+        ashape(std::move(as)), bshape(std::move(bs)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    const int64_t batch = numel(out_batch.empty() ? std::vector<int>{1} : out_batch);
+    const int64_t M = a->shape[a->ndim() - 2], K = a->shape[a->ndim() - 1], N = b->shape[b->ndim() - 1];
+    auto gshape = out_batch; gshape.push_back((int)M); gshape.push_back((int)N);
+    auto gc = gin(g, gshape);
+    auto da_shape = out_batch; da_shape.push_back((int)M); da_shape.push_back((int)K);
+    auto db_shape = out_batch; db_shape.push_back((int)K); db_shape.push_back((int)N);
+    const int64_t a_bs = all_ones(pa) && batch > 1 ? 0 : M * K, b_bs = all_ones(pb) && batch > 1 ? 0 : K * N;
+    auto dA = gemm(gc, b, batch, M, K, N, false, true, M * N, b_bs, da_shape);   // G B^T
+    auto dB = gemm(a, gc, batch, K, N, M, true, false, a_bs, M * N, db_shape);   // A^T G
+    return {sum_to_batch(dA, pa, out_batch, ashape), sum_to_batch(dB, pb, out_batch, bshape)};
+  }
+  void release_variables() override { a = b = nullptr; }
+};
+
+inline std::shared_ptr<Tensor> manual_matmul(const std::shared_ptr<Tensor>& _a, const std::shared_ptr<Tensor>& _b) {
+  using namespace dgshim;
+  if (_a->ndim() < 2 || _b->ndim() < 2) throw std::runtime_error("matmul: both operands need at least 2 dims");
+  const int M = _a->shape[_a->ndim() - 2], K = _a->shape[_a->ndim() - 1], N = _b->shape[_b->ndim() - 1];
+  if (K != _b->shape[_b->ndim() - 2]) throw std::runtime_error("matmul: inner dims differ");
+  std::vector<int> ba(_a->shape.begin(), _a->shape.end() - 2), bb(_b->shape.begin(), _b->shape.end() - 2);
+  const size_t nb = std::max(ba.size(), bb.size());
+  std::vector<int> pa(nb - ba.size(), 1), pb(nb - bb.size(), 1), out_batch;
+  pa.insert(pa.end(), ba.begin(), ba.end());
+  pb.insert(pb.end(), bb.begin(), bb.end());
+  for (size_t i = 0; i < nb; ++i) {
+    if (pa[i] != pb[i] && pa[i] != 1 && pb[i] != 1) throw std::runtime_error("matmul: batch dims are not broadcast-compatible");
+    out_batch.push_back(std::max(pa[i], pb[i]));
+  }
+  auto a = expand_batch(_a, pa, out_batch), b = expand_batch(_b, pb, out_batch);
+  const int64_t batch = numel(out_batch.empty() ? std::vector<int>{1} : out_batch);
+  auto out_shape = out_batch; out_shape.push_back(M); out_shape.push_back(N);
+  const int64_t a_bs = all_ones(pa) && batch > 1 ? 0 : (int64_t)M * K, b_bs = all_ones(pb) && batch > 1 ? 0 : (int64_t)K * N;
+  auto out = gemm(a, b, batch, M, N, K, false, false, a_bs, b_bs, out_shape);
+  attach<MatmulBackward>(out, {_a, _b}, a, b, pa, pb, out_batch, _a->shape, _b->shape);
+  return out;
+}
+inline std::shared_ptr<Tensor> matmul(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b) {
+  return manual_matmul(a, b);
+}

@@ -1,0 +1,288 @@
+// Third part of the op set: views, concat, scale_n_shift, masks, softmax, reductions, losses.
+#pragma once
+#include "dg_ops2.h"
+
+// ------------------------------------------------------------------ transpose / view / reshape
+struct TransposeBackward : Node {
+  int d0, d1;
+  TransposeBackward(int a, int b) : d0(a), d1(b) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override { return {g[0]->_transpose(d0, d1)}; }  // a view; consumers normalise
+};
+inline std::shared_ptr<Tensor> transpose(const std::shared_ptr<Tensor>& a, int dim0 = -2, int dim1 = -1) {
+  if (a->ndim() < 2) throw std::runtime_error("transpose: needs at least 2 dims");
+  auto out = a->_transpose(dim0, dim1);
+  dgshim::attach<TransposeBackward>(out, {a}, dim0, dim1);
+  return out;
+}
+
+struct ViewBackward : Node {
+  std::vector<int> in_shape;
+  explicit ViewBackward(std::vector<int> s) : in_shape(std::move(s)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override { return {g[0]->_reshape(in_shape)}; }
+};
+inline std::shared_ptr<Tensor> view(const std::shared_ptr<Tensor>& a, const std::vector<int>& new_shape) {
+  auto out = a->_view(new_shape);   // throws when non-contiguous
+  dgshim::attach<ViewBackward>(out, {a}, a->shape);
+  return out;
+}
+inline std::shared_ptr<Tensor> reshape(const std::shared_ptr<Tensor>& a, const std::vector<int>& new_shape) {
+  auto out = a->_reshape(new_shape);
+  dgshim::attach<ViewBackward>(out, {a}, a->shape);
+  return out;
+}
+
+// ------------------------------------------------------------------ concat (src/concat.h)
+namespace dgshim {
+// copy `src` (any strides) into the sub-block of contiguous `dst` that starts at `start` along `dim`
+inline void copy_block(const TP& dst, const TP& src, int dim, int start, bool into_dst) {
+  std::vector<int64_t> shape(src->shape.begin(), src->shape.end());
+  auto dstr = make_strides(dst->shape);
+  std::vector<int64_t> ds(dstr.begin(), dstr.end()), ss(src->strides.begin(), src->strides.end());
+  const int64_t off = (int64_t)start * dstr[dim];
+  if (into_dst)
+    check(dg_strided_copy(0, dst->dev_rw() + off, ds.data(), src->dev_ro(), ss.data(), shape.data(), (int)shape.size(),
+                          stream()), "strided copy");
+  else  // gather the block of dst (here: the gradient) into contiguous src
+    check(dg_strided_copy(0, src->dev_rw(), ss.data(), dst->dev_ro() + off, ds.data(), shape.data(), (int)shape.size(),
+                          stream()), "strided copy");
+}
+}  // namespace dgshim
+
+struct ConcatBackward : Node {
+  int dim, na, nb;
+  std::vector<int> ashape, bshape, out_shape;
+  ConcatBackward(int d, std::vector<int> as, std::vector<int> bs, std::vector<int> os)
+      : dim(d), na(as[d]), nb(bs[d]), ashape(std::move(as)), bshape(std::move(bs)), out_shape(std::move(os)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, out_shape);
+    auto ga = make(ashape), gb = make(bshape);
+    copy_block(gc, ga, dim, 0, false);
+    copy_block(gc, gb, dim, na, false);
+    return {ga, gb};
+  }
+};
+// Join along the second-to-last dim (axis 0) or the last dim (otherwise).
+inline std::shared_ptr<Tensor> concat(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& b, int axis) {
+  using namespace dgshim;
+  if (a->ndim() < 2 || a->ndim() != b->ndim()) throw std::runtime_error("concat: operands need the same rank >= 2");
+  const int dim = axis == 0 ? a->ndim() - 2 : a->ndim() - 1;
+  for (int i = 0; i < a->ndim(); ++i)
+    if (i != dim && a->shape[i] != b->shape[i]) throw std::runtime_error("concat: shapes differ outside the joined dim");
+  auto out_shape = a->shape;
+  out_shape[dim] += b->shape[dim];
+  auto out = make(out_shape);
+  copy_block(out, a, dim, 0, true);
+  copy_block(out, b, dim, a->shape[dim], true);
+  attach<ConcatBackward>(out, {a, b}, dim, a->shape, b->shape, out_shape);
+  return out;
+}
+
+// ------------------------------------------------------------------ scale_n_shift (src/cool_ops.h)
+struct ScaleAndShiftBackward : Node {
+  dgshim::TP x, gamma;
+  ScaleAndShiftBackward(dgshim::TP x_, dgshim::TP g_) : x(std::move(x_)), gamma(std::move(g_)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, x->shape);
+    int64_t B, r, c;
+    brc(x->shape, B, r, c);
+    auto gx = ew(EW_MUL, x->shape, gc, gamma, nullptr, nullptr, BC_ROW);
+    auto gg = reduce_cols(ew(EW_MUL, x->shape, gc, x), 1, B * r, c, RED_SUM, {1, (int)c});
+    auto gb = reduce_cols(gc, 1, B * r, c, RED_SUM, {1, (int)c});
+    return {gx, gg, gb};
+  }
+  void release_variables() override { x = gamma = nullptr; }
+};
+// Per-feature affine x * gamma[j] + beta[j] (the in-bounds reading of src/cool_ops.h:90-92).
+inline std::shared_ptr<Tensor> scale_n_shift(const std::shared_ptr<Tensor>& x, const std::shared_ptr<Tensor>& gamma,
+                                             const std::shared_ptr<Tensor>& beta) {
+  using namespace dgshim;
+  const int c = x->shape.back();
+  if (gamma->size() != c || beta->size() != c) throw std::runtime_error("scale_n_shift: one gamma/beta entry per feature");
+  auto xc = contiguous(x), gc = contiguous(gamma), bc = contiguous(beta);
+  auto out = ew(EW_SCALE_SHIFT, x->shape, xc, gc, bc, nullptr, BC_ROW, BC_ROW);
+  attach<ScaleAndShiftBackward>(out, {x, gamma, beta}, xc, gc);
+  return out;
+}
+
+// ------------------------------------------------------------------ masks and softmax
+inline std::shared_ptr<Tensor> bool_mask(const std::shared_ptr<Tensor>& a, const std::shared_ptr<Tensor>& m) {
+  using namespace dgshim;
+  same_shape(a, m, "bool_mask");
+  auto mc = contiguous(m);
+  auto out = ew(EW_MASK_FILL, a->shape, contiguous(a), mc, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, -1e9f);
+  attach<BoolMaskBackward>(out, {a}, mc, (int)EW_MASK_BWD, 0.f);
+  return out;
+}
+
+struct CausalMaskBackward : Node {
+  std::vector<int> shape;
+  explicit CausalMaskBackward(std::vector<int> s) : shape(std::move(s)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    return {ew(EW_CAUSAL_BWD, shape, gin(g, shape))};
+  }
+};
+inline std::shared_ptr<Tensor> causal_mask(const std::shared_ptr<Tensor>& a) {
+  using namespace dgshim;
+  if (a->ndim() < 2) throw std::runtime_error("causal_mask: needs at least 2 dims");
+  auto out = ew(EW_CAUSAL_FILL, a->shape, contiguous(a), nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, -1e9f);
+  attach<CausalMaskBackward>(out, {a}, a->shape);
+  return out;
+}
+
+struct SoftmaxBackward : Node {
+  dgshim::TP out;
+  explicit SoftmaxBackward(dgshim::TP o) : out(std::move(o)) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gc = gin(g, out->shape);
+    auto gx = make(out->shape);
+    int64_t B, r, c;
+    brc(out->shape, B, r, c);
+    check(dg_softmax_bwd(0, gx->dev_rw(), gc->dev_ro(), out->dev_ro(), nullptr, 0, 1.0f, B * r, r, c, stream()), "softmax bwd");
+    return {gx};
+  }
+};
+inline std::shared_ptr<Tensor> softmax(const std::shared_ptr<Tensor>& a) {
+  using namespace dgshim;
+  auto ac = contiguous(a);
+  auto out = make(a->shape);
+  int64_t B, r, c;
+  brc(a->shape, B, r, c);
+  check(dg_softmax_fwd(0, out->dev_rw(), ac->dev_ro(), nullptr, 0, 1.0f, B * r, r, c, stream()), "softmax fwd");
+  attach<SoftmaxBackward>(out, {a}, out->alias(out->shape, out->strides));
+  return out;
+}
+
+// ------------------------------------------------------------------ reductions (src/sum.h, mean.h, var.h, std.h)
+struct SumBackward : Node {
+  std::vector<int> shape;
+  bool rows;
+  float scale;
+  SumBackward(std::vector<int> s, bool r, float sc) : shape(std::move(s)), rows(r), scale(sc) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto oshape = shape;
+    oshape[shape.size() - (rows ? 2 : 1)] = 1;
+    auto out = ew(EW_COPY_Y, shape, nullptr, gin(g, oshape), nullptr, nullptr, rows ? BC_COLS : BC_ROWS);
+    if (scale != 1.0f) out = ew(EW_MUL_S, shape, out, nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, scale);
+    return {out};
+  }
+};
+struct MeanBackward : SumBackward { using SumBackward::SumBackward; };
+
+namespace dgshim {
+inline TP reduce_last2(const TP& a, bool rows, int mode, TP* mean = nullptr) {
+  if (a->ndim() < 2) throw std::runtime_error("reduction needs at least 2 dims");
+  auto ac = contiguous(a);
+  int64_t B, r, c;
+  brc(a->shape, B, r, c);
+  auto oshape = a->shape;
+  oshape[a->ndim() - (rows ? 2 : 1)] = 1;
+  return rows ? reduce_cols(ac, B, r, c, mode, oshape, mean) : reduce_rows(ac, B * r, c, mode, oshape, mean);
+}
+}  // namespace dgshim
+
+// Keepdim sum over one of the last two dims; `axis` is a real (possibly negative) index.
+inline std::shared_ptr<Tensor> sum(const std::shared_ptr<Tensor>& a, int axis) {
+  using namespace dgshim;
+  const int ax = axis < 0 ? axis + a->ndim() : axis;
+  if (ax != a->ndim() - 1 && ax != a->ndim() - 2) throw std::runtime_error("sum: only the last two dims can be reduced");
+  const bool rows = ax == a->ndim() - 2;
+  auto out = reduce_last2(a, rows, RED_SUM);
+  attach<SumBackward>(out, {a}, a->shape, rows, 1.0f);
+  return out;
+}
+// axis 0 = second-to-last dim, anything else = last dim (src/mean.h:64)
+inline std::shared_ptr<Tensor> mean(const std::shared_ptr<Tensor>& a, int axis) {
+  using namespace dgshim;
+  const bool rows = axis == 0;
+  auto out = reduce_last2(a, rows, RED_MEAN);
+  attach<MeanBackward>(out, {a}, a->shape, rows, 1.0f / (float)a->shape[a->ndim() - (rows ? 2 : 1)]);
+  return out;
+}
+
+struct VarBackward : Node {
+  dgshim::TP a, mu, sd;
+  bool rows;
+  int n;
+  VarBackward(dgshim::TP a_, dgshim::TP mu_, dgshim::TP sd_, bool r, int n_)
+      : a(std::move(a_)), mu(std::move(mu_)), sd(std::move(sd_)), rows(r), n(n_) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto oshape = a->shape;
+    oshape[a->ndim() - (rows ? 2 : 1)] = 1;
+    auto gc = gin(g, oshape);
+    const int m = rows ? BC_COLS : BC_ROWS;
+    if (!sd) return {ew(EW_VAR_BWD, a->shape, a, mu, gc, nullptr, m, m, BC_SAME, 2.0f / n)};
+    return {ew(EW_STD_BWD, a->shape, a, mu, gc, sd, m, m, m, 1.0f / n, 1e-8f)};
+  }
+  void release_variables() override { a = mu = sd = nullptr; }
+};
+struct StdDevBackward : VarBackward { using VarBackward::VarBackward; };
+
+// Biased (divide by N) keepdim variance (src/var.h:82,98)
+inline std::shared_ptr<Tensor> var(const std::shared_ptr<Tensor>& a, int axis) {
+  using namespace dgshim;
+  const bool rows = axis == 0;
+  TP mu;
+  auto out = reduce_last2(a, rows, RED_VAR, &mu);
+  attach<VarBackward>(out, {a}, contiguous(a), mu, nullptr, rows, a->shape[a->ndim() - (rows ? 2 : 1)]);
+  return out;
+}
+// sqrt of the biased variance; gradient (a - mu) / (N (sigma + 1e-8)) (src/std.h:32-35)
+inline std::shared_ptr<Tensor> std_dev(const std::shared_ptr<Tensor>& a, int axis) {
+  using namespace dgshim;
+  const bool rows = axis == 0;
+  TP mu;
+  auto out = reduce_last2(a, rows, RED_STD, &mu);
+  attach<StdDevBackward>(out, {a}, contiguous(a), mu, out->alias(out->shape, out->strides), rows, a->shape[a->ndim() - (rows ? 2 : 1)]);
+  return out;
+}
+
+// ------------------------------------------------------------------ losses (src/loss.h)
+struct CrossEntropyBackward : Node {
+  dgshim::TP pred, target;
+  int n;
+  CrossEntropyBackward(dgshim::TP p, dgshim::TP t, int n_) : pred(std::move(p)), target(std::move(t)), n(n_) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    return {ew(EW_XENT_PROB_BWD, pred->shape, pred, target, contiguous(g[0]), nullptr, BC_SAME, BC_SCALAR, BC_SAME, 1.0f / n),
+            nullptr};
+  }
+};
+// -sum(t * log(p + 1e-8)) / n on probabilities, n = rows * classes (src/loss.h:27-52)
+inline std::shared_ptr<Tensor> cross_entropy(const std::shared_ptr<Tensor>& pred, const std::shared_ptr<Tensor>& target) {
+  using namespace dgshim;
+  same_shape(pred, target, "cross_entropy");
+  auto pc = contiguous(pred), tc = contiguous(target);
+  const int n = pred->size();
+  auto lp = ew(EW_LOG_EPS, pred->shape, pc, nullptr, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, 1e-8f);
+  auto out = sum_all(ew(EW_MUL, pred->shape, lp, tc), -1.0f / n, {1, 1});
+  attach<CrossEntropyBackward>(out, {pred, target}, pc, tc, n);
+  return out;
+}
+
+struct MseBackward : Node {
+  dgshim::TP pred, target;
+  int n;
+  MseBackward(dgshim::TP p, dgshim::TP t, int n_) : pred(std::move(p)), target(std::move(t)), n(n_) {}
+  dgshim::Grads apply(const dgshim::Grads& g) override {
+    using namespace dgshim;
+    auto gp = ew(EW_MSE_BWD, pred->shape, pred, target, contiguous(g[0]), nullptr, BC_SAME, BC_SCALAR, BC_SAME, 2.0f / n);
+    return {gp, ew(EW_NEG, pred->shape, gp)};
+  }
+};
+// sum((p - t)^2) / n -> [1, 1] (src/loss.h:55-103)
+inline std::shared_ptr<Tensor> mse(const std::shared_ptr<Tensor>& pred, const std::shared_ptr<Tensor>& target) {
+  using namespace dgshim;
+  same_shape(pred, target, "mse");
+  auto pc = contiguous(pred), tc = contiguous(target);
+  const int n = pred->size();
+  auto d = ew(EW_SUB, pred->shape, pc, tc);
+  auto out = sum_all(ew(EW_MUL, pred->shape, d, d), 1.0f / n, {1, 1});
+  attach<MseBackward>(out, {pred, target}, pc, tc, n);
+  return out;
+}

@@ -38,6 +38,10 @@ class _Proxy:
             key = name
             if name == "dg_elementwise":
                 key = f"dg_elementwise[{L._EW_NAMES[args[0]]}]"
+            elif name == "dg_gemm_sm100":
+                g = args[0]._obj
+                lay = ("n" if g.a_kmajor else "t") + ("t" if g.b_kmajor else "n")
+                key = f"dg_gemm_sm100[{lay} {g.M}x{g.N}x{g.K}" + (f" b{g.batch}]" if g.batch > 1 else "]")
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             rc = fn(*args)
