@@ -28,8 +28,8 @@ sys.path.insert(0, ROOT)
 
 CONFIGS = {
     # name: (preset, global_batch, seq_len, micro_batch, dtype, lr)
-    "gpt350m": ("gpt350m", 64, 1024, 8, "bf16", 3e-4),
-    "gpt1p3b": ("gpt1p3b", 32, 2048, 2, "bf16", 2e-4),
+    "gpt350m": ("gpt350m", 64, 1024, 64, "bf16", 3e-4),
+    "gpt1p3b": ("gpt1p3b", 32, 2048, 8, "bf16", 2e-4),
     "toy": ("toy", 8, 32, 8, "fp32", 3e-4),
 }
 

@@ -39,47 +39,54 @@ int dg_flags_wait(const int* flags, int n, int epoch, int* status, long long wai
 // pads[r][offset] = value for every rank r (system-scope release store).
 int dg_flags_signal(int* const* pads_dev, int world, int offset, int value, cudaStream_t stream);
 
-// F3: all-gather -> GEMM.  C[M, N_local] = gather_rows(A_shard)[M, K] * B[K, N_local]
-//   Every rank holds rows [rank*M/W, (rank+1)*M/W) of A. A gather role inside the same kernel
-//   copies peer rows into this rank's full-A buffer chunk by chunk and raises per-chunk flags;
-//   the GEMM role's TMA producer waits on the flag of the chunk it is about to load and starts
-//   with the locally owned rows.
+// F3: all-gather -> GEMM.  D[M, N] = gather_rows(A)[M, K] * B + bias   (bf16 in, bf16 out)
+//   Every rank holds rows [rank*M/W, (rank+1)*M/W) of A inside its own gathered-A buffer (a
+//   symmetric [M, K] allocation). Copy CTAs of the same kernel pull the other ranks' row blocks
+//   from their buffers into this rank's buffer, 128 rows at a time, and raise one flag per block;
+//   the GEMM CTAs' TMA producer waits on the flag of the block it is about to load and the tile
+//   order starts with the locally owned rows, then follows the order in which blocks arrive.
+//   Flag pad layout (int32): ready[world] then read_done[world].
 typedef struct {
-  const void* const* a_shard_ptrs; // device array [world]: every rank's A shard [M/W, K] bf16 (row stride lda)
-  void* a_full;                    // this rank's gathered A [M, K] bf16 (row stride lda); own rows already in place or copied too
-  const void* B;                   // [K, N] (b_kmajor=0) or [N, K] (b_kmajor=1) bf16
-  void* D;                         // [M, N] bf16/fp32
-  const void* bias;
+  void* const* a_full_ptrs;        // device array [world]: every rank's gathered-A buffer [M, K] (row stride lda)
+  void* a_local;                   // this rank's entry of that array (host-visible copy, for the tensor map)
+  const void* B;                   // [K, N] (b_kmajor = 0) or [N, K] (b_kmajor = 1), bf16, row stride ldb
+  void* D;                         // [M, N] bf16, row stride ldd
+  const void* bias;                // [N] or null
   int64_t M, N, K, lda, ldb, ldd;
-  int b_kmajor, out_dtype, bias_dtype, epi;
+  int b_kmajor, bias_dtype, epi;
   int rank, world;
-  int* chunk_flags;                // device int [M / chunk_rows], local memory
-  int* const* flag_ptrs;           // peer flag pads (ready handshake), int32
-  int flag_offset;                 // first of `world` ints in each pad used by this call
-  int epoch;
-  int copy_ctas;                   // CTAs reserved for the gather role (0: default)
+  int* chunk_flags;                // device int [M / 128], this GPU's memory, epoch-valued
+  int* const* flag_ptrs;           // device array [world]: every rank's flag pad
+  int epoch;                       // strictly increasing per call on these buffers
+  int copy_ctas;                   // CTAs reserved for the gather role (0: default 16)
   int* status;
   long long wait_cycles;
 } dg_ag_gemm_args;
 int dg_ag_gemm(const dg_ag_gemm_args* args, cudaStream_t stream);
 
-// F4: GEMM -> reduce-scatter.  C_local[M/W, N] = sum over ranks of (A_r[M, K_local] * B_r[K_local, N]) rows of this rank.
-//   Finished fp32-accumulated tiles are written as bf16 partials straight into the owner rank's
-//   staging slot for this source, followed by a per-tile flag; reducer CTAs of the same kernel
-//   sum the `world` partials of each owned tile in fp32 and write the output.
+// F4: GEMM -> reduce-scatter.  D_r[M/W, N] = sum over ranks s of (A_s[M, K_s] * B_s[K_s, N]) rows of rank r (+ bias + residual)
+//   Finished fp32-accumulated tiles are rounded to bf16 and written straight into the owner rank's
+//   staging slot for this source (peer stores from the epilogue), followed by a per-tile flag;
+//   reducer CTAs of the same kernel sum the `world` partials of each owned tile in fp32, in rank
+//   order, and write the output. Tiles are produced in an order rotated by rank so that every
+//   destination receives data throughout the kernel.
 typedef struct {
-  const void* A;                   // [M, K_local] bf16 row-major (lda)
-  const void* B;                   // [K_local, N] or [N, K_local] bf16
-  void* const* staging_ptrs;       // device array [world]: every rank's staging buffer [world][M/W, N] bf16
-  int* const* tile_flag_ptrs;      // device array [world]: every rank's per-(source, tile) flags
-  void* D;                         // [M/W, N] bf16/fp32 output of this rank
-  const void* bias;                // added once by the owner
-  const void* residual;            // [M/W, N] added by the owner (may alias D)
+  const void* A;                   // [M, K] bf16 row-major (lda): this rank's K-slice of the activations
+  const void* B;                   // [K, N] or [N, K] bf16 (ldb): this rank's K-slice of the weight
+  void* const* dest_slots;         // device array [world]: for destination d, d's staging slot for this source rank
+  int* const* tile_flag_ptrs;      // device array [world]: every rank's tile flags [world][tiles_per_rank]
+  int* const* done_flag_ptrs;      // device array [world]: every rank's done[world]
+  const void* staging;             // this rank's staging [world][M/W, N] bf16
+  const int* tile_flags;           // this rank's tile flags
+  const int* done_flags;           // this rank's done[world]
+  void* D;                         // [M/W, N] bf16 (ldd)
+  const void* bias;                // [N] or null, added once by the owner
+  const void* residual;            // [M/W, N] bf16 or null (may alias D)
   int64_t M, N, K, lda, ldb, ldd;
-  int b_kmajor, out_dtype, bias_dtype;
+  int b_kmajor, bias_dtype;
   int rank, world;
   int epoch;
-  int reduce_ctas;                 // CTAs reserved for the reducer role (0: default)
+  int reduce_ctas;                 // CTAs reserved for the reducer role (0: default 16)
   int* status;
   long long wait_cycles;
 } dg_gemm_rs_args;

@@ -246,8 +246,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
       for (int64_t t = cta_rank; t < total_tiles && ok; t += cta_count) {
         int64_t b, mt, nt;
         decode_tile(t, m_tiles, n_tiles, b, mt, nt);
+        if constexpr (GATE_A || SCATTER_D) mt = (mt + p.m_tile_rotate) % m_tiles;
         if constexpr (GATE_A) {
-          mt = (mt + p.m_tile_rotate) % m_tiles;
           // every chunk that overlaps rows [mt*128, mt*128+128) must have arrived
           const int64_t c0 = (mt * kBM) / p.rows_per_chunk;
           int64_t last_row = mt * kBM + kBM - 1;
@@ -348,7 +348,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
     for (int64_t t = cta_rank; t < total_tiles; t += cta_count) {
       int64_t b, mt, nt;
       decode_tile(t, m_tiles, n_tiles, b, mt, nt);
-      if constexpr (GATE_A) mt = (mt + p.m_tile_rotate) % m_tiles;
+      if constexpr (GATE_A || SCATTER_D) mt = (mt + p.m_tile_rotate) % m_tiles;
       ok = bounded_wait(&tfull_bar[acc], (acc_phase_bits >> acc) & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;

@@ -1,0 +1,200 @@
+"""Tensor parallelism with sequence-parallel activations (Megatron layout) on the fused kernels.
+
+Between tensor-parallel regions the activations are sharded on tokens: every rank holds
+``tokens / W`` rows of LayerNorm / residual tensors. A column-parallel linear therefore starts
+with an all-gather of rows and a row-parallel linear ends with a reduce-scatter of rows; both
+collectives run INSIDE the GEMM kernel (``dg_ag_gemm`` / ``dg_gemm_rs``) over NVLink peer
+memory. ``comm="collective"`` swaps in torch.distributed collectives + the plain GEMM: the NCCL
+baseline on GPUs and the only path on CPU (gloo), where sharding and gradient logic are tested.
+
+Forward / backward pairing (x: [T/W, K] row shard, full X: [T, K]):
+
+  column-parallel   Y = gather(x) W_c            fwd  all-gather -> GEMM
+                    dx = scatter(dY W_c^T)        bwd  GEMM -> reduce-scatter
+                    dW_c = gather(x)^T dY              (gathered X is kept from the forward)
+  row-parallel      y = scatter(X W_r)            fwd  GEMM -> reduce-scatter
+                    dX = gather(dy) W_r^T         bwd  all-gather -> GEMM
+                    dW_r = X^T gather(dy)              (gathered dy is left in the buffer by the kernel)
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib as L
+from ..ops import kernels as K
+from ..tensor import Node, Tensor, get_grad_edge
+from .symm import SymmBuffer
+
+
+class AgGemmArgs(C.Structure):
+    _fields_ = [("a_full_ptrs", C.c_void_p), ("a_local", C.c_void_p), ("B", C.c_void_p), ("D", C.c_void_p),
+                ("bias", C.c_void_p),
+                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64),
+                ("ldd", C.c_int64),
+                ("b_kmajor", C.c_int), ("bias_dtype", C.c_int), ("epi", C.c_int), ("rank", C.c_int), ("world", C.c_int),
+                ("chunk_flags", C.c_void_p), ("flag_ptrs", C.c_void_p), ("epoch", C.c_int), ("copy_ctas", C.c_int),
+                ("status", C.c_void_p), ("wait_cycles", C.c_longlong)]
+
+
+class GemmRsArgs(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("dest_slots", C.c_void_p), ("tile_flag_ptrs", C.c_void_p),
+                ("done_flag_ptrs", C.c_void_p), ("staging", C.c_void_p), ("tile_flags", C.c_void_p),
+                ("done_flags", C.c_void_p), ("D", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
+                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64),
+                ("ldd", C.c_int64),
+                ("b_kmajor", C.c_int), ("bias_dtype", C.c_int), ("rank", C.c_int), ("world", C.c_int),
+                ("epoch", C.c_int), ("reduce_ctas", C.c_int), ("status", C.c_void_p), ("wait_cycles", C.c_longlong)]
+
+
+def _bind(lib):
+    if getattr(lib, "_dg_tp_bound", False):
+        return lib
+    lib.dg_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.c_void_p]
+    lib.dg_ag_gemm.restype = C.c_int
+    lib.dg_gemm_rs.argtypes = [C.POINTER(GemmRsArgs), C.c_void_p]
+    lib.dg_gemm_rs.restype = C.c_int
+    lib._dg_tp_bound = True
+    return lib
+
+
+class GatherBuffer:
+    """Symmetric [M, K] bf16 buffer in which every rank owns a block of rows; the fused
+    all-gather->GEMM fills the other blocks and leaves the gathered matrix behind."""
+
+    def __init__(self, M: int, Kd: int, ctx: "TPContext"):
+        self.M, self.K, self.ctx = M, Kd, ctx
+        self.buf = SymmBuffer(M * Kd, torch.bfloat16, ctx.device, ctx.group)
+        self.full = self.buf.tensor.view(M, Kd)
+        rows = M // ctx.world
+        self.mine = self.full[ctx.rank * rows:(ctx.rank + 1) * rows]
+        self.pad = SymmBuffer(2 * ctx.world, torch.int32, ctx.device, ctx.group)
+        self.chunk_flags = torch.zeros(M // 128, dtype=torch.int32, device=ctx.device)
+        self.epoch = 0
+
+
+class ScatterBuffer:
+    """Staging for the fused GEMM->reduce-scatter: [W sources][M/W, N] bf16 per rank + flags."""
+
+    def __init__(self, M: int, N: int, ctx: "TPContext"):
+        self.M, self.N, self.ctx = M, N, ctx
+        W, rows = ctx.world, M // ctx.world
+        self.staging = SymmBuffer(M * N, torch.bfloat16, ctx.device, ctx.group, zero=False)
+        tiles = (rows // 128) * ((N + 255) // 256)
+        self.tile_flags = SymmBuffer(W * tiles, torch.int32, ctx.device, ctx.group)
+        self.done = SymmBuffer(W, torch.int32, ctx.device, ctx.group)
+        slot_bytes = rows * N * 2
+        # where this rank's partial rows for destination d go: d's staging + my slot
+        self.dest_slots = torch.tensor([p + ctx.rank * slot_bytes for p in self.staging.ptrs], dtype=torch.int64,
+                                       device=ctx.device)
+        self.epoch = 0
+
+
+class TPContext:
+    """Process-group facts + buffer cache shared by the tensor-parallel layers of one model."""
+
+    def __init__(self, group=None, comm: str = "fused", device=None, wait_seconds: float = 20.0, comm_ctas: int = 16):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                                 else torch.device("cpu"))
+        self.comm = comm if self.device.type == "cuda" else "collective"
+        self.wait_cycles = int(wait_seconds * 1.9e9)
+        self.comm_ctas = comm_ctas
+        self._gather: dict = {}
+        self._scatter: dict = {}
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def gather_buffer(self, key, M, Kd) -> GatherBuffer:
+        b = self._gather.get((key, M, Kd))
+        if b is None:
+            b = self._gather[(key, M, Kd)] = GatherBuffer(M, Kd, self)
+        return b
+
+    def scatter_buffer(self, key, M, N) -> ScatterBuffer:
+        b = self._scatter.get((key, M, N))
+        if b is None:
+            b = self._scatter[(key, M, N)] = ScatterBuffer(M, N, self)
+        return b
+
+    def check_status(self) -> int:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+        return code
+
+
+# ----------------------------------------------------------------------------- raw fused ops
+def ag_gemm(ctx: TPContext, x_shard: torch.Tensor, w: torch.Tensor, bias=None, *, trans_w=False, key="ag",
+            epi: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Y = gather_rows(x_shard) @ W (+ bias). x_shard [M/W, K]; W [K, N] (or [N, K] with trans_w).
+    Returns (Y [M, N], gathered X [M, K] - valid until the next call with the same key)."""
+    rows, Kd = x_shard.shape
+    M = rows * ctx.world
+    N = w.shape[0] if trans_w else w.shape[1]
+    if ctx.comm != "fused":
+        if ctx.world > 1:
+            full = torch.empty(M, Kd, dtype=x_shard.dtype, device=x_shard.device)
+            dist.all_gather_into_tensor(full, x_shard.contiguous(), group=ctx.group)
+        else:
+            full = x_shard
+        return K.gemm2d(full, w, trans_b=trans_w, bias=bias, epi=epi), full
+    gb = ctx.gather_buffer(key, M, Kd)
+    K.assign_(gb.mine, x_shard) if x_shard.data_ptr() != gb.mine.data_ptr() else None
+    gb.epoch += 1
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x_shard.device)
+    a = AgGemmArgs()
+    a.a_full_ptrs, a.a_local = gb.buf.ptrs_dev.data_ptr(), gb.full.data_ptr()
+    a.B, a.D, a.bias = w.data_ptr(), out.data_ptr(), L.ptr(bias)
+    a.M, a.N, a.K, a.lda, a.ldb, a.ldd = M, N, Kd, Kd, w.stride(0), N
+    a.b_kmajor, a.bias_dtype, a.epi = (1 if trans_w else 0), (L.dtype_code(bias.dtype) if bias is not None else 0), epi
+    a.rank, a.world = ctx.rank, ctx.world
+    a.chunk_flags, a.flag_ptrs = gb.chunk_flags.data_ptr(), gb.pad.ptrs_dev.data_ptr()
+    a.epoch, a.copy_ctas = gb.epoch, ctx.comm_ctas
+    a.status, a.wait_cycles = ctx.status.data_ptr(), ctx.wait_cycles
+    L.check(_bind(L.load()).dg_ag_gemm(C.byref(a), L.stream_ptr()), "dg_ag_gemm")
+    K._cnt()
+    return out, gb.full
+
+
+def gemm_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, *, trans_w=False, key="rs"):
+    """y_shard[M/W, N] = scatter_rows(sum over ranks of x @ W) (+ bias + residual). x [M, K_local]."""
+    M, Kd = x.shape
+    N = w.shape[0] if trans_w else w.shape[1]
+    rows = M // ctx.world
+    if ctx.comm != "fused":
+        part = K.gemm2d(x, w, trans_b=trans_w)
+        if ctx.world > 1:
+            out = torch.empty(rows, N, dtype=part.dtype, device=part.device)
+            if part.is_cuda:
+                dist.reduce_scatter_tensor(out, part, group=ctx.group)
+            else:
+                dist.all_reduce(part, group=ctx.group)
+                out = part[ctx.rank * rows:(ctx.rank + 1) * rows].contiguous()
+        else:
+            out = part
+        if bias is not None:
+            out = K.ew("ADD", out, K.cast(bias.reshape(-1), out.dtype), ymode=L.BC_ROW, out=out)
+        if residual is not None:
+            out = K.ew("ADD", out, residual, out=out)
+        return out
+    sb = ctx.scatter_buffer(key, M, N)
+    sb.epoch += 1
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
+    a = GemmRsArgs()
+    a.A, a.B = x.data_ptr(), w.data_ptr()
+    a.dest_slots = sb.dest_slots.data_ptr()
+    a.tile_flag_ptrs, a.done_flag_ptrs = sb.tile_flags.ptrs_dev.data_ptr(), sb.done.ptrs_dev.data_ptr()
+    a.staging, a.tile_flags, a.done_flags = (sb.staging.tensor.data_ptr(), sb.tile_flags.tensor.data_ptr(),
+                                             sb.done.tensor.data_ptr())
+    a.D, a.bias, a.residual = out.data_ptr(), L.ptr(bias), L.ptr(residual)
+    a.M, a.N, a.K, a.lda, a.ldb, a.ldd = M, N, Kd, x.stride(0), w.stride(0), N
+    a.b_kmajor, a.bias_dtype = (1 if trans_w else 0), (L.dtype_code(bias.dtype) if bias is not None else 0)
+    a.rank, a.world, a.epoch, a.reduce_ctas = ctx.rank, ctx.world, sb.epoch, ctx.comm_ctas
+    a.status, a.wait_cycles = ctx.status.data_ptr(), ctx.wait_cycles
+    L.check(_bind(L.load()).dg_gemm_rs(C.byref(a), L.stream_ptr()), "dg_gemm_rs")
+    K._cnt()
+    return out

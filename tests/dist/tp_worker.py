@@ -1,0 +1,66 @@
+"""Worker for the fused tensor-parallel GEMM tests (launched with torch.distributed.run).
+Checks dg_ag_gemm and dg_gemm_rs against fp32 PyTorch math on gathered data, twice in a row
+(buffers and epoch-valued flags are reused), for both weight layouts."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import dummygrad_b200 as dg  # noqa: E402
+from dummygrad_b200.parallel import dist as D  # noqa: E402
+from dummygrad_b200.parallel import tp  # noqa: E402
+
+
+def gather(t):
+    parts = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, t.contiguous())
+    return parts
+
+
+def main():
+    rank, world, device = D.init()
+    dg.set_default_device(device)
+    ctx = tp.TPContext(comm="fused", device=device, wait_seconds=5.0)
+    torch.manual_seed(100 + rank)
+    for (M, Kd, N) in [(128 * world * 2, 256, 512), (128 * world * 3, 512, 768 + 8), (128 * world, 1024, 256)]:
+        for trans_w in (False, True):
+            for rep in range(2):
+                # ---- all-gather -> GEMM
+                x = torch.randn(M // world, Kd, device=device).to(torch.bfloat16)
+                w = (torch.randn(N, Kd, device=device) * 0.1).to(torch.bfloat16)
+                dist.broadcast(w, 0)
+                wl = w if trans_w else w.t().contiguous()
+                bias = torch.randn(N, device=device).to(torch.bfloat16)
+                dist.broadcast(bias, 0)
+                y, xfull = tp.ag_gemm(ctx, x, wl, bias, trans_w=trans_w, key=("t", trans_w))
+                torch.cuda.synchronize()
+                assert ctx.check_status() == 0
+                xs = torch.cat(gather(x))
+                assert torch.equal(xfull, xs), "gathered activations differ"
+                ref = xs.float() @ w.float().t() + bias.float()
+                err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+                assert err < 2e-2, f"ag_gemm M{M} K{Kd} N{N} trans{trans_w} rep{rep}: rel err {err}"
+                # ---- GEMM -> reduce-scatter (each rank holds a K-slice)
+                xk = torch.randn(M, Kd, device=device).to(torch.bfloat16)
+                wk = (torch.randn(N, Kd, device=device) * 0.1).to(torch.bfloat16)
+                wkl = wk if trans_w else wk.t().contiguous()
+                res = torch.randn(M // world, N, device=device).to(torch.bfloat16)
+                out = tp.gemm_rs(ctx, xk, wkl, bias, res, trans_w=trans_w, key=("s", trans_w))
+                torch.cuda.synchronize()
+                assert ctx.check_status() == 0
+                part = xk.float() @ wk.float().t()
+                dist.all_reduce(part)
+                rows = M // world
+                ref = part[rank * rows:(rank + 1) * rows] + bias.float() + res.float()
+                err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+                assert err < 3e-2, f"gemm_rs M{M} K{Kd} N{N} trans{trans_w} rep{rep}: rel err {err}"
+    dist.barrier()
+    if rank == 0:
+        print(f"TP_WORKER_OK world={world}")
+    D.shutdown()
+
+
+if __name__ == "__main__":
+    main()
