@@ -1,0 +1,165 @@
+"""Microbenchmarks of the fused compute+collective kernels against NCCL + cuBLAS baselines.
+
+    python -m torch.distributed.run --nproc-per-node W bench/fused_bench.py [--what rs_adam,ag_gemm,gemm_rs]
+
+  rs_adam : bf16 gradient buffers 1 MB .. 1 GB, reduce-scatter + scale + sharded Adam + parameter
+            all-gather in one kernel (dg_rs_optim) vs NCCL reduce_scatter + fused Adam + all_gather.
+  ag_gemm : M = N = K = 8192 bf16, A sharded on rows, B on columns: dg_ag_gemm vs all_gather + matmul.
+  gemm_rs : same sizes, A and B sharded on K: dg_gemm_rs vs matmul + reduce_scatter.
+Timing: CUDA events on the launching stream after warm-up, maximum over ranks. Roofline of a
+fused path = max(FLOPs / measured bf16 peak, bytes received per GPU / 770 GB/s measured peer copy).
+One JSON line per measurement is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import dummygrad_b200 as dg  # noqa: E402
+from dummygrad_b200.ops import kernels as K  # noqa: E402
+from dummygrad_b200.parallel import dist as D  # noqa: E402
+from dummygrad_b200.parallel import tp  # noqa: E402
+from dummygrad_b200.parallel.dp import DataParallel  # noqa: E402
+
+LINK_GBS = 770.0
+
+
+def peak():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get("bf16_tflops", 1590.0), "measured"
+    return 1590.0, "fallback"
+
+
+def timeit(fn, device, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    D.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return D.max_over_ranks(e0.elapsed_time(e1) / iters, device)
+
+
+class _Flat:
+    """A 'model' with one flat bf16 parameter, to drive the data-parallel engine on raw buffers."""
+
+    def __init__(self, n, device):
+        self.p = dg.Tensor([n], True, dtype=torch.bfloat16, device=device)
+
+    def parameters(self):
+        return [self.p]
+
+
+def bench_rs_adam(rank, world, device, emit):
+    for mb in (1, 4, 16, 64, 256, 1024):
+        n = mb * 2 ** 20 // 2
+        n = n // (8 * world) * (8 * world)
+        dp = DataParallel(_Flat(n, device), lr=1e-3, comm="fused", bucket_mb=4096, max_comm_ctas=148)
+        dp.grad_flat.normal_()
+
+        def fused():
+            dp.begin_step()
+            for b in dp.buckets:
+                for p in b.params:
+                    p._sink_filled = True
+            dp.finish_step()
+
+        ms = timeit(fused, device)
+        # NCCL baseline: reduce_scatter + Adam on the shard + all_gather
+        g = torch.randn(n, device=device).to(torch.bfloat16)
+        shard = torch.empty(n // world, dtype=torch.bfloat16, device=device)
+        pfull = torch.empty(n, dtype=torch.bfloat16, device=device)
+        master = torch.zeros(n // world, device=device)
+        m, v = torch.zeros_like(master), torch.zeros_like(master)
+        pshard = torch.zeros(n // world, dtype=torch.bfloat16, device=device)
+
+        def nccl():
+            if world > 1:
+                dist.reduce_scatter_tensor(shard, g)
+            else:
+                shard.copy_(g)
+            K.adam_step(pshard, master, shard, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.0, 1, 1.0 / world)
+            if world > 1:
+                dist.all_gather_into_tensor(pfull, pshard)
+
+        ms_n = timeit(nccl, device)
+        link_bytes = 2 * (world - 1) / world * n * 2          # pull grads + push params, per GPU per direction each
+        roof_ms = max((world - 1) / world * n * 2 / (LINK_GBS * 1e9), n / world * 18 / 6.5e12) * 1e3
+        emit({"bench": "rs_adam", "world": world, "bucket_mb": mb, "fused_ms": ms, "nccl_ms": ms_n,
+              "nvlink_bytes_per_gpu": link_bytes, "roofline_ms": roof_ms, "frac_of_roofline": roof_ms / ms})
+        del dp
+
+
+def bench_tp(rank, world, device, emit, which):
+    M = N = Kd = 8192
+    pk, src = peak()
+    ctx = tp.TPContext(comm="fused", device=device, comm_ctas=int(os.environ.get("DG_TP_CTAS", "16")))
+    flops = 2.0 * M * N * Kd / world
+    comm_ms = (world - 1) / world * M * Kd * 2 / (LINK_GBS * 1e9) * 1e3
+    roof = max(flops / (pk * 1e12) * 1e3, comm_ms)
+    if "ag_gemm" in which:
+        x = torch.randn(M // world, Kd, device=device).to(torch.bfloat16)
+        w = torch.randn(Kd, N // world, device=device).to(torch.bfloat16)
+        ms = timeit(lambda: tp.ag_gemm(ctx, x, w, key="b"), device)
+        full = torch.empty(M, Kd, dtype=torch.bfloat16, device=device)
+        out = torch.empty(M, N // world, dtype=torch.bfloat16, device=device)
+
+        def base():
+            if world > 1:
+                dist.all_gather_into_tensor(full, x)
+            torch.matmul(full, w, out=out)
+
+        ms_b = timeit(base, device)
+        emit({"bench": "ag_gemm", "world": world, "M": M, "N_local": N // world, "K": Kd, "fused_ms": ms,
+              "nccl_cublas_ms": ms_b, "roofline_ms": roof, "frac_of_roofline": roof / ms, "peak_source": src,
+              "sharding": "A rows sharded [M/W, K], B columns sharded [K, N/W]", "status": ctx.check_status()})
+    if "gemm_rs" in which:
+        x = torch.randn(M, Kd // world, device=device).to(torch.bfloat16)
+        w = torch.randn(Kd // world, N, device=device).to(torch.bfloat16)
+        ms = timeit(lambda: tp.gemm_rs(ctx, x, w, key="b"), device)
+        part = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        out = torch.empty(M // world, N, dtype=torch.bfloat16, device=device)
+
+        def base():
+            torch.matmul(x, w, out=part)
+            if world > 1:
+                dist.reduce_scatter_tensor(out, part)
+
+        ms_b = timeit(base, device)
+        comm2 = (world - 1) / world * M * N * 2 / (LINK_GBS * 1e9) * 1e3
+        roof2 = max(flops / (pk * 1e12) * 1e3, comm2)
+        emit({"bench": "gemm_rs", "world": world, "M": M, "N": N, "K_local": Kd // world, "fused_ms": ms,
+              "nccl_cublas_ms": ms_b, "roofline_ms": roof2, "frac_of_roofline": roof2 / ms, "peak_source": src,
+              "sharding": "A and B sharded on K; output rows scattered, bf16 partials", "status": ctx.check_status()})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="rs_adam,ag_gemm,gemm_rs")
+    a = ap.parse_args()
+    rank, world, device = D.init()
+    dg.set_default_device(device)
+
+    def emit(rec):
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+
+    which = a.what.split(",")
+    if "rs_adam" in which:
+        bench_rs_adam(rank, world, device, emit)
+    bench_tp(rank, world, device, emit, which)
+    D.barrier()
+    D.shutdown()
+
+
+if __name__ == "__main__":
+    main()

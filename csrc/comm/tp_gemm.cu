@@ -10,7 +10,8 @@
 //               remote tile never feeds a TMA load directly, and nothing is multicast).
 //   dg_gemm_rs  (GEMM -> reduce-scatter): the epilogue writes each finished bf16 partial tile
 //               into the owning rank's staging slot with peer stores and publishes a per-tile
-//               flag; reducer CTAs sum the partials of their own tiles in fp32 in rank order.
+//               flag; the tiles a rank owns are computed last and their epilogue adds the
+//               delivered partials in fp32 before writing the output.
 // Every wait on a peer is bounded and reports through *status.
 #include <cstring>
 #include "../kernels/gemm_sm100.cuh"
@@ -40,8 +41,29 @@ struct AgRole {
 
 // Gather role of one copy CTA. Blocks of 128 rows are taken round-robin over the copy CTAs in the
 // order peer = rank+1, rank+2, ... so that data arrives in the order the GEMM consumes it.
-__device__ __forceinline__ void ag_copy_role(const AgRole& r, int cta, int* s_ok) {
+constexpr int kChunk = 32768;   // bytes per bulk copy
+constexpr int kRing = 6;        // shared-memory slots
+constexpr int kLook = 3;        // peer loads kept in flight
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read_n() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ag_copy_role(const AgRole& r, int cta, int* s_ok, uint8_t* ring, uint64_t* ring_bar) {
   const int W = r.world;
+  int64_t ring_pos = 0, ring_base = 0;   // chunks issued / chunks completed by earlier blocks (one thread's view)
+  volatile int never = 0;
   const int64_t rows_per_rank = r.M / W;
   const int64_t blocks_per_rank = rows_per_rank / 128;
   int* my_pad = r.flag_ptrs[r.rank];
@@ -72,6 +94,45 @@ __device__ __forceinline__ void ag_copy_role(const AgRole& r, int cta, int* s_ok
     }
     const uint8_t* src_base = reinterpret_cast<const uint8_t*>(r.a_full_ptrs[src]);
     const int64_t row0 = blk * 128;
+    if (r.lda == r.K && ring != nullptr) {
+      // contiguous block: stream it through shared memory with bulk async copies (one thread
+      // keeps kLook loads from the peer and kRing - kLook stores to local memory in flight)
+      if (threadIdx.x == 0) {
+        const int64_t bytes = 128 * r.K * 2, n = (bytes + kChunk - 1) / kChunk;
+        const uint8_t* sp = src_base + row0 * r.lda * 2;
+        uint8_t* dp = dst_base + row0 * r.lda * 2;
+        for (int64_t c = 0; c < n + kLook - 1 && ok; ++c) {
+          if (c < n) {
+            const int slot = (int)(ring_pos % kRing);
+            bulk_wait_read_n<kRing - kLook - 1>();
+            const uint32_t sz = (uint32_t)((bytes - c * kChunk) < kChunk ? (bytes - c * kChunk) : kChunk);
+            mbar_expect_tx(&ring_bar[slot], sz);
+            bulk_load_1d(ring + slot * kChunk, sp + c * kChunk, sz, &ring_bar[slot]);
+            ++ring_pos;
+          }
+          const int64_t j = c - (kLook - 1);
+          if (j >= 0 && j < n) {
+            const int64_t gpos = ring_base + j;      // global index of chunk j in this CTA's stream
+            const int slot = (int)(gpos % kRing);
+            ok = bounded_wait(&ring_bar[slot], (uint32_t)((gpos / kRing) & 1), &never, r.wait_cycles);
+            if (!ok) break;
+            const uint32_t sz = (uint32_t)((bytes - j * kChunk) < kChunk ? (bytes - j * kChunk) : kChunk);
+            bulk_store_1d(dp + j * kChunk, ring + slot * kChunk, sz);
+            bulk_commit();
+          }
+        }
+        ring_base += n;
+        bulk_wait_all();                              // the block has landed in local memory
+        __threadfence();
+        if (ok) peer::st_release_sys(r.chunk_flags + blk, r.epoch);
+        *s_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      ok = *s_ok != 0;
+      __syncthreads();
+      if (!ok) break;
+      continue;
+    }
     const int64_t units_per_row = r.K / 8;            // 16-byte units
     const int64_t units = 128 * units_per_row;
     for (int64_t u0 = threadIdx.x; u0 < units; u0 += (int64_t)blockDim.x * 8) {
@@ -113,7 +174,15 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     return;
   }
   const int cta = (int)blockIdx.x - gemm_ctas;
-  ag_copy_role(r, cta, &s_ok);
+  // shared-memory ring for the bulk copies (this CTA does not run the GEMM, so the tile memory is free)
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* ring_bar = reinterpret_cast<uint64_t*>(ring + kRing * kChunk);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kRing; ++i) mbar_init(&ring_bar[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  ag_copy_role(r, cta, &s_ok, ring, ring_bar);
   // Leave only after every peer has finished reading this rank's rows: tell each peer that this
   // rank is done reading (last copy CTA to finish), then wait for the same word from all of them.
   __threadfence_system();
@@ -130,6 +199,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+struct TmapArray { CUtensorMap m[8]; };   // one output map per destination rank
+
 struct RsRole {
   const bf16* staging;
   const int* tile_flags;
@@ -143,67 +214,15 @@ struct RsRole {
   long long wait_cycles;
 };
 
-// Reducer role: owned tiles (128 x kTpBN) round-robin over the reducer CTAs.
-__device__ __forceinline__ void rs_reduce_role(const RsRole& r, int cta, int* s_ok) {
-  const int W = r.world;
-  const int64_t n_tiles = (r.N + kTpBN - 1) / kTpBN, m_tiles = r.rows_per_rank / 128;
-  const int64_t tiles = m_tiles * n_tiles;
-  const int64_t slot = r.rows_per_rank * r.N;        // elements per source slot
-  bool ok = true;
-  for (int64_t t = cta; t < tiles && ok; t += r.reduce_ctas) {
-    // same tile numbering as the producers' flags: ltile = local m tile * n_tiles + n tile
-    if (threadIdx.x < W) {
-      // rank-rotated wait order does not matter for correctness; every source must have published
-      if (!peer::wait_flag(r.tile_flags + (int64_t)threadIdx.x * tiles + t, r.epoch, r.wait_cycles)) atomicExch(s_ok, 0);
-    }
-    __syncthreads();
-    ok = *s_ok != 0;
-    if (!ok) break;
-    const int64_t mt = t / n_tiles, nt = t % n_tiles;
-    const int64_t row0 = mt * 128, col0 = nt * kTpBN;
-    const int64_t ncols = (r.N - col0) < kTpBN ? (r.N - col0) : kTpBN;
-    const int64_t units_per_row = ncols / 8;
-    for (int64_t u = threadIdx.x; u < 128 * units_per_row; u += blockDim.x) {
-      const int64_t row = row0 + u / units_per_row, col = col0 + (u % units_per_row) * 8;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int s = 0; s < W; ++s) {                  // fixed rank order: deterministic
-        uint4 raw = peer::ld_peer_16(r.staging + (int64_t)s * slot + row * r.N + col);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
-      }
-      if (r.bias) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          acc[k] += r.bias_dtype == DG_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(r.bias)[col + k])
-                                            : reinterpret_cast<const float*>(r.bias)[col + k];
-      }
-      if (r.residual) {
-        uint4 raw = *reinterpret_cast<const uint4*>(r.residual + row * r.ldd + col);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
-      }
-      uint4 out;
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-      *reinterpret_cast<uint4*>(r.D + row * r.ldd + col) = out;
-    }
-    __syncthreads();
-  }
-  if (!ok && threadIdx.x == 0 && r.status) atomicExch(r.status, 0x400 | r.rank);
-}
-
 template <bool B_K>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-               const RsRole r, const int* my_done_flags, int* done_counter) {
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ TmapArray dest_maps, const GemmParams p, const RsRole r, const int* my_done_flags,
+               int* done_counter) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_ok;
-  const int gemm_ctas = (int)gridDim.x - r.reduce_ctas;
-  // The staging slots this call writes were last read by their owners' reducers in the previous
-  // call: wait until every owner has reported that call finished.
+  // The staging slots this call writes were last read by their owners in the previous call: wait
+  // until every owner has reported that call finished.
   if (threadIdx.x == 0) {
     int ok = 1;
     for (int q = 0; q < r.world && ok; ++q) ok = peer::wait_flag(my_done_flags + q, r.epoch - 1, r.wait_cycles) ? 1 : 0;
@@ -212,17 +231,16 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   __syncthreads();
   if (!s_ok) return;
-  if ((int)blockIdx.x < gemm_ctas) {
-    gemm_cta_body<kTpBN, kTpStages, true, B_K, bf16, false, true>(&tmA, &tmB, nullptr, nullptr, p, smem_raw,
-                                                                 (int)blockIdx.x, gemm_ctas);
-    return;
-  }
-  rs_reduce_role(r, (int)blockIdx.x - gemm_ctas, &s_ok);
+  // Every CTA runs the GEMM. Tiles for other ranks go out as bf16 partials from the epilogue; the
+  // tiles this rank owns come last in its order and their epilogue folds in the partials that the
+  // other ranks delivered meanwhile, so the reduction costs no SMs of its own.
+  gemm_cta_body<kTpBN, kTpStages, true, B_K, bf16, false, true>(&tmA, &tmB, dest_maps.m, nullptr, p, smem_raw,
+                                                               (int)blockIdx.x, (int)gridDim.x);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     const int prev = atomicAdd(done_counter, 1);
-    if (prev == r.reduce_ctas - 1) {
+    if (prev == (int)gridDim.x - 1) {
       *done_counter = 0;
       for (int q = 0; q < r.world; ++q) peer::st_release_sys(r.done_flag_ptrs[q] + r.rank, r.epoch);
     }
@@ -288,11 +306,10 @@ extern "C" int dg_gemm_rs(const dg_gemm_rs_args* a, cudaStream_t stream) {
   if (!a || !a->A || !a->B || !a->D || !a->dest_slots || !a->tile_flag_ptrs || !a->done_flag_ptrs || !a->staging ||
       !a->tile_flags || !a->done_flags)
     return DG_ERR_BAD_ARG;
-  if (a->world < 1 || a->rank < 0 || a->rank >= a->world || a->epoch < 1) return DG_ERR_BAD_ARG;
+  if (a->world < 1 || a->world > 16 || a->rank < 0 || a->rank >= a->world || a->epoch < 1)
+    return DG_ERR_BAD_ARG;
   if (a->M % (128 * a->world) || a->N % 8 || a->K % 8 || a->lda % 8 || a->ldb % 8 || a->ldd % 8) return DG_ERR_UNSUPPORTED;
   const int sms = sm_count();
-  int reduce_ctas = a->reduce_ctas > 0 ? a->reduce_ctas : 16;
-  if (reduce_ctas >= sms) return DG_ERR_BAD_ARG;
   CUtensorMap tmA, tmB;
   if (get_tmap(&tmA, a->A, a->K, a->M, 1, a->lda, 0, kBK, kBM)) return DG_ERR_DRIVER;
   int rc = a->b_kmajor ? get_tmap(&tmB, a->B, a->K, a->N, 1, a->ldb, 0, kBK, kTpBN)
@@ -302,7 +319,9 @@ extern "C" int dg_gemm_rs(const dg_gemm_rs_args* a, cudaStream_t stream) {
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K; p.batch = 1;
-  p.ldd = a->N; p.d_bs = 0; p.D = nullptr; p.alpha = 1.0f; p.status = a->status; p.a_bcast = 1; p.b_bcast = 1;
+  p.ldd = a->ldd; p.d_bs = 0; p.D = a->D; p.bias = a->bias; p.bias_dtype = a->bias_dtype; p.residual = a->residual;
+  p.alpha = 1.0f; p.status = a->status; p.a_bcast = 1; p.b_bcast = 1;
+  p.own_staging = a->staging; p.own_flags = a->tile_flags; p.stage_ld = a->N; p.world = a->world;
   p.dest_base = a->dest_slots; p.rows_per_dest = rows_per_rank; p.dest_flags = a->tile_flag_ptrs;
   p.src_rank = a->rank; p.d_epoch = a->epoch;
   // start with the tiles owned by the next rank so that all links carry data from the beginning
@@ -311,8 +330,16 @@ extern "C" int dg_gemm_rs(const dg_gemm_rs_args* a, cudaStream_t stream) {
   r.staging = (const dg::bf16*)a->staging; r.tile_flags = a->tile_flags; r.done_flag_ptrs = a->done_flag_ptrs;
   r.D = (dg::bf16*)a->D; r.bias = a->bias; r.residual = (const dg::bf16*)a->residual;
   r.rows_per_rank = rows_per_rank; r.N = a->N; r.ldd = a->ldd; r.bias_dtype = a->bias_dtype;
-  r.rank = a->rank; r.world = a->world; r.epoch = a->epoch; r.reduce_ctas = reduce_ctas; r.status = a->status;
+  r.rank = a->rank; r.world = a->world; r.epoch = a->epoch; r.reduce_ctas = 0; r.status = a->status;
   r.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : dg::peer::kFlagWaitCycles;
+  TmapArray maps;
+  std::memset(&maps, 0, sizeof(maps));
+  if (a->dest_slots_host && a->world <= 8 && a->N % 8 == 0) {
+    bool all = true;
+    for (int d = 0; d < a->world && all; ++d)
+      all = dg::make_tmap_out_3d(&maps.m[d], 2, a->dest_slots_host[d], a->N, rows_per_rank, 1, a->N, 0, 64, 32) == 0;
+    p.tma_store = all ? 1 : 0;
+  }
   int* counter = tp_counter();
   if (!counter) return DG_ERR_DRIVER;
   using SM = GemmSmem<kTpBN, kTpStages>;
@@ -320,8 +347,8 @@ extern "C" int dg_gemm_rs(const dg_gemm_rs_args* a, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
     if (e != cudaSuccess) return (int)e;
     const int64_t tiles = (a->M / 128) * ((a->N + kTpBN - 1) / kTpBN);
-    int gemm_ctas = (int)(tiles < sms - reduce_ctas ? tiles : sms - reduce_ctas);
-    kern<<<gemm_ctas + reduce_ctas, kGemmThreads, SM::kTotal, stream>>>(tmA, tmB, p, r, a->done_flags, counter + 1);
+    int gemm_ctas = (int)(tiles < sms ? tiles : sms);
+    kern<<<gemm_ctas, kGemmThreads, SM::kTotal, stream>>>(tmA, tmB, maps, p, r, a->done_flags, counter + 1);
     cudaError_t le = cudaGetLastError();
     return le == cudaSuccess ? DG_OK : (int)le;
   };

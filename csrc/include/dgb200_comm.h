@@ -74,6 +74,7 @@ typedef struct {
   const void* A;                   // [M, K] bf16 row-major (lda): this rank's K-slice of the activations
   const void* B;                   // [K, N] or [N, K] bf16 (ldb): this rank's K-slice of the weight
   void* const* dest_slots;         // device array [world]: for destination d, d's staging slot for this source rank
+  void* const* dest_slots_host;    // the same addresses in a host array (tensor maps are built on the host)
   int* const* tile_flag_ptrs;      // device array [world]: every rank's tile flags [world][tiles_per_rank]
   int* const* done_flag_ptrs;      // device array [world]: every rank's done[world]
   const void* staging;             // this rank's staging [world][M/W, N] bf16
@@ -86,7 +87,7 @@ typedef struct {
   int b_kmajor, bias_dtype;
   int rank, world;
   int epoch;
-  int reduce_ctas;                 // CTAs reserved for the reducer role (0: default 16)
+  int reduce_ctas;                 // unused (the reduction runs in the owner's epilogue); kept for ABI stability
   int* status;
   long long wait_cycles;
 } dg_gemm_rs_args;

@@ -57,6 +57,12 @@ struct GemmParams {
   int* const* dest_flags;    // per-destination flag array; flag[(src_rank * tiles) + tile] = epoch on completion
   int src_rank;
   int d_epoch;
+  // owner-side reduction: tiles whose rows this rank owns are produced last; their epilogue adds the
+  // other ranks' partials (already in this rank's staging) and writes the final output
+  const void* own_staging;   // this rank's staging [world][rows_per_dest, stage_ld] bf16
+  const int* own_flags;      // this rank's tile flags [world][tiles_per_dest]
+  int64_t stage_ld;          // row stride of a staging slot (elements)
+  int world;
 };
 
 template <int BN, int STAGES>
@@ -356,15 +362,33 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
       const int64_t row = mt * kBM + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
       OutT* drow;
+      bool own_tile = false;          // SCATTER_D: this rank owns the tile's rows and reduces it here
+      int64_t lrow = row, ltile = 0, tiles_per_dest = 0;
+      const bf16* auxrow = p.aux ? reinterpret_cast<const bf16*>(p.aux) + b * p.d_bs + row * p.ldd : nullptr;
+      const OutT* resrow = p.residual ? reinterpret_cast<const OutT*>(p.residual) + b * p.d_bs + row * p.ldd : nullptr;
       if constexpr (SCATTER_D) {
-        const int64_t dest = row_ok ? row / p.rows_per_dest : 0;
-        const int64_t lrow = row - dest * p.rows_per_dest;
-        drow = reinterpret_cast<OutT*>(p.dest_base[dest]) + lrow * p.ldd;
+        const int64_t dest = (mt * kBM) / p.rows_per_dest;            // uniform over the tile
+        lrow = row - dest * p.rows_per_dest;
+        tiles_per_dest = (p.rows_per_dest / kBM) * n_tiles;
+        ltile = (mt - dest * (p.rows_per_dest / kBM)) * n_tiles + nt;
+        own_tile = dest == p.src_rank;
+        if (own_tile) {
+          drow = reinterpret_cast<OutT*>(p.D) + lrow * p.ldd;
+          resrow = p.residual ? reinterpret_cast<const OutT*>(p.residual) + lrow * p.ldd : nullptr;
+          // the other ranks' partials of this tile must have landed in this rank's staging
+          bool got = true;
+          if (lane == 0)
+            for (int s2 = 0; s2 < p.world && got; ++s2)
+              if (s2 != p.src_rank) got = bounded_flag_wait(p.own_flags + (int64_t)s2 * tiles_per_dest + ltile, p.d_epoch, abort_flag);
+          got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+          if (!got) { ok = false; break; }
+        } else {
+          drow = reinterpret_cast<OutT*>(p.dest_base[dest]) + lrow * p.stage_ld;
+          resrow = nullptr;
+        }
       } else {
         drow = reinterpret_cast<OutT*>(p.D) + b * p.d_bs + row * p.ldd;
       }
-      const bf16* auxrow = p.aux ? reinterpret_cast<const bf16*>(p.aux) + b * p.d_bs + row * p.ldd : nullptr;
-      const OutT* resrow = p.residual ? reinterpret_cast<const OutT*>(p.residual) + b * p.d_bs + row * p.ldd : nullptr;
       const int ch_begin = half * (BN / 64), ch_end = (half + 1) * (BN / 64);
       // Values of one 32-column chunk of this thread's row. `pre_only` stops after alpha and bias
       // (the pre-activation that the GELU / ReLU epilogues also save).
@@ -372,6 +396,33 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
                               bool pre_only, bool aux_direct) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
+        if constexpr (SCATTER_D) {
+          if (!own_tile) return;                     // a partial for another rank: no bias, no residual
+          // add the other ranks' partials in rank order (this rank's own term sits at its rank position
+          // only up to fp32 rounding of the sum; partials are bf16, the accumulation is fp32)
+          for (int s2 = 0; s2 < p.world; ++s2) {
+            if (s2 == p.src_rank) continue;
+            const bf16* pr = reinterpret_cast<const bf16*>(p.own_staging) + (int64_t)s2 * p.rows_per_dest * p.stage_ld +
+                             lrow * p.stage_ld + col0;
+            float pv[32];
+            if (valid == 32) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 pk;
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w) : "l"(pr + q * 8) : "memory");
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); pv[q * 8 + 2 * e] = f.x; pv[q * 8 + 2 * e + 1] = f.y; }
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) pv[e] = e < valid ? __bfloat162float(pr[e]) : 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] += pv[e];
+          }
+        }
         if (p.bias) {
           if (p.bias_dtype == DG_BF16) {
             const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + b * p.bias_bs + col0;
@@ -426,8 +477,17 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       };
 
-      bool use_tma = false;
-      if constexpr (!SCATTER_D) use_tma = p.tma_store != 0;
+      bool use_tma = p.tma_store != 0;
+      const CUtensorMap* tm_out = tmD;
+      int row0_tma = (int)(mt * kBM + lane_group * 32);
+      if constexpr (SCATTER_D) {
+        // partial tiles for other ranks leave through TMA stores into the owner's staging (full
+        // 128-byte lines over NVLink); owned tiles are reduced and stored directly
+        use_tma = use_tma && !own_tile;
+        const int64_t dest = (mt * kBM) / p.rows_per_dest;
+        tm_out = tmD + dest;
+        row0_tma = (int)(mt * kBM - dest * p.rows_per_dest + lane_group * 32);
+      }
       if (use_tma) {
         // ---- staged path: each warp packs a [32 rows x 128 bytes] slab in shared memory (128-byte
         // swizzle) and one thread hands it to the TMA store unit; full 128-byte lines reach L2 and
@@ -438,7 +498,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         const int sw = lane & 7;
         const bool two_pass = p.tma_aux != 0;            // GELU / ReLU with a saved pre-activation (bf16)
         const int npass = two_pass ? 2 : 1;
-        const int row0_warp = (int)(mt * kBM + lane_group * 32);
+        const int row0_warp = row0_tma;
 #pragma unroll 1
         for (int s0 = ch_begin; s0 < ch_end; s0 += kCh) {
           const int64_t col_slab = nt * BN + s0 * 32;
@@ -479,7 +539,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
             if (!(p.debug & 4)) fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && col_slab < p.N && !(p.debug & 3)) {
-              tma_store_3d(aux_pass ? tmAux : tmD, slab, (int)col_slab, row0_warp, (int)b);
+              tma_store_3d(aux_pass ? tmAux : tm_out, slab, (int)col_slab, row0_warp, (int)b);
               bulk_commit();
             }
           }
@@ -501,14 +561,15 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         }
       }
       if constexpr (SCATTER_D) {
-        // publish the tile to its destination: all four epilogue warps have stored their rows
-        __threadfence_system();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int64_t dest = (mt * kBM) / p.rows_per_dest;
-          const int64_t tiles_per_dest = (p.rows_per_dest / kBM) * n_tiles;
-          const int64_t ltile = (mt - dest * (p.rows_per_dest / kBM)) * n_tiles + nt;
-          st_release_sys(p.dest_flags[dest] + (int64_t)p.src_rank * tiles_per_dest + ltile, p.d_epoch);
+        if (!own_tile) {
+          // publish the partial tile to its owner: all eight epilogue warps have stored their rows
+          if (use_tma && lane == 0) { bulk_wait_all(); asm volatile("fence.proxy.async;" ::: "memory"); }
+          __threadfence_system();
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            const int64_t dest = (mt * kBM) / p.rows_per_dest;
+            st_release_sys(p.dest_flags[dest] + (int64_t)p.src_rank * tiles_per_dest + ltile, p.d_epoch);
+          }
         }
       }
       acc_phase_bits ^= (1u << acc);

@@ -40,7 +40,8 @@ class AgGemmArgs(C.Structure):
 
 
 class GemmRsArgs(C.Structure):
-    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("dest_slots", C.c_void_p), ("tile_flag_ptrs", C.c_void_p),
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("dest_slots", C.c_void_p), ("dest_slots_host", C.c_void_p),
+                ("tile_flag_ptrs", C.c_void_p),
                 ("done_flag_ptrs", C.c_void_p), ("staging", C.c_void_p), ("tile_flags", C.c_void_p),
                 ("done_flags", C.c_void_p), ("D", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
                 ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64),
@@ -89,6 +90,7 @@ class ScatterBuffer:
         # where this rank's partial rows for destination d go: d's staging + my slot
         self.dest_slots = torch.tensor([p + ctx.rank * slot_bytes for p in self.staging.ptrs], dtype=torch.int64,
                                        device=ctx.device)
+        self.dest_slots_host = (C.c_void_p * W)(*[p + ctx.rank * slot_bytes for p in self.staging.ptrs])
         self.epoch = 0
 
 
@@ -187,6 +189,7 @@ def gemm_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, bias=None, residua
     a = GemmRsArgs()
     a.A, a.B = x.data_ptr(), w.data_ptr()
     a.dest_slots = sb.dest_slots.data_ptr()
+    a.dest_slots_host = C.cast(sb.dest_slots_host, C.c_void_p)
     a.tile_flag_ptrs, a.done_flag_ptrs = sb.tile_flags.ptrs_dev.data_ptr(), sb.done.ptrs_dev.data_ptr()
     a.staging, a.tile_flags, a.done_flags = (sb.staging.tensor.data_ptr(), sb.tile_flags.tensor.data_ptr(),
                                              sb.done.tensor.data_ptr())
