@@ -111,6 +111,8 @@ def run_ours(args) -> dict:
     assert gbatch % world == 0, "global batch must divide over the ranks"
     lbatch = gbatch // world
     micro = min(micro, lbatch)
+    if args.parallel.startswith("tp"):
+        return run_tp(args, rank, world, device, preset, gbatch, seq, micro, lr)
     dg.manual_seed(1234)   # same seed on every rank: identical initial weights
     model = dg.models.build_preset(preset, dtype=dtype, device=device)
     trainer = Trainer(model, micro_batch=micro, lr=lr, weight_decay=0.1 if args.config != "toy" else 0.0,
@@ -176,6 +178,81 @@ def run_ours(args) -> dict:
                 "d2h_bytes_per_step": 4},
         "loss_first": first, "loss_last": last, "params": model.num_parameters(),
     }
+    D.barrier()
+    D.shutdown()
+    return out if rank == 0 else {}
+
+
+def run_tp(args, rank, world, device, preset, gbatch, seq, micro, lr) -> dict:
+    """Tensor-parallel (x data-parallel) arm: --parallel tpN or tpNdpM."""
+    import torch
+    import dummygrad_b200 as dg
+    from dummygrad_b200.ops import kernels as K
+    from dummygrad_b200.parallel import dist as D
+    from dummygrad_b200.parallel.trainer import TPTrainer
+    spec = args.parallel
+    tp_size = int(spec[2:].split("dp")[0])
+    dp_size = world // tp_size
+    assert tp_size * dp_size == world and gbatch % dp_size == 0
+    dg.manual_seed(1234 + rank % tp_size)       # shards differ inside a group, replicas match across groups
+    tr = TPTrainer(preset, tp_size=tp_size, micro_batch=micro, seq_len=seq, lr=lr, comm=args.comm, device=device)
+    # replicated parameters must start identical inside a tensor-parallel group
+    if tp_size > 1:
+        import torch.distributed as dist
+        for p in tr.model.parameters():
+            if p.name in ("tp_replicated", "tp_identical"):
+                dist.broadcast(p.data, src=(rank // tp_size) * tp_size, group=tr.tp_group)
+    vocab = tr.model.vocab_size
+    rb = gbatch // dp_size
+    gen = torch.Generator().manual_seed(1000 + rank // tp_size)
+    n_sets = 2
+    host_ids = [torch.randint(0, vocab, (rb, seq), generator=gen).pin_memory() for _ in range(n_sets)]
+    host_tgt = [torch.randint(0, vocab, (rb * seq,), generator=gen).pin_memory() for _ in range(n_sets)]
+    dev_ids = [t.to(device) for t in host_ids]
+    dev_tgt = [t.to(device) for t in host_tgt]
+    stage_i = torch.empty_like(dev_ids[0])
+    stage_t = torch.empty_like(dev_tgt[0])
+    losses = []
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize(); D.barrier(); torch.cuda.synchronize()
+        sampler = ClockSampler(device.index or 0)
+        sampler.start()
+        l0 = K.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize(); D.barrier(); torch.cuda.synchronize()
+        return D.max_over_ranks(e0.elapsed_time(e1), device), sampler.stop(), K.launch_count - l0
+
+    def dev_step(i):
+        losses.append(tr.step_device(dev_ids[i % n_sets], dev_tgt[i % n_sets]))
+
+    def e2e_step(i):
+        stage_i.copy_(host_ids[i % n_sets], non_blocking=True)
+        stage_t.copy_(host_tgt[i % n_sets], non_blocking=True)
+        return tr.step_device(stage_i, stage_t).item()
+
+    ms, clocks, launches = timed(dev_step, args.steps, args.warmup)
+    tr.check()
+    ms2, _, _ = timed(e2e_step, args.steps, max(1, min(args.warmup, 2)))
+    tr.check()
+    tokens = gbatch * seq
+    out = {"metric": "train tokens/sec (device-timed, max over ranks)", "value": tokens * args.steps / (ms / 1e3),
+           "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "bf16", "data": "synthetic uniform random tokens, random-init weights", "impl": "ours",
+           "config": {"model": preset, "global_batch": gbatch, "seq_len": seq, "micro_batch": micro,
+                      "parallelism": spec, "comm": tr.ctx.comm, "optimizer": "adamw (fp32 master)",
+                      "l2": "no explicit flush: each step streams >10 GB (L2 is 126 MB)"},
+           "clocks": clocks, "gpu_launches": launches,
+           "e2e": {"value": tokens * args.steps / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / args.steps,
+                   "h2d_bytes_per_step": int(host_ids[0].numel() * 8 + host_tgt[0].numel() * 8), "d2h_bytes_per_step": 4},
+           "loss_first": float(losses[0].item()) * tp_size, "loss_last": float(losses[-1].item()) * tp_size}
     D.barrier()
     D.shutdown()
     return out if rank == 0 else {}
@@ -288,6 +365,7 @@ def main() -> None:
     ap.add_argument("--comm", default="fused", choices=["fused", "collective"])
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--bucket-mb", type=float, default=64.0)
+    ap.add_argument("--parallel", default="dp", help="dp (default), tpN or tpNdpM, e.g. tp8, tp2dp4")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:

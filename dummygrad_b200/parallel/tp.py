@@ -97,10 +97,11 @@ class ScatterBuffer:
 class TPContext:
     """Process-group facts + buffer cache shared by the tensor-parallel layers of one model."""
 
-    def __init__(self, group=None, comm: str = "fused", device=None, wait_seconds: float = 20.0, comm_ctas: int = 16):
+    def __init__(self, group=None, comm: str = "fused", device=None, wait_seconds: float = 20.0, comm_ctas: int = 16,
+                 single: bool = False):
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and not single) else 1
+        self.rank = dist.get_rank(group) if (dist.is_initialized() and not single) else 0
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                                  else torch.device("cpu"))
         self.comm = comm if self.device.type == "cuda" else "collective"

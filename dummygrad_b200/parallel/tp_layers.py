@@ -1,0 +1,294 @@
+"""Autograd nodes and modules for tensor parallelism with sequence-parallel activations.
+
+``column_parallel`` and ``row_parallel`` are differentiable ops on token-sharded activations
+whose collectives run inside the GEMM kernels (see :mod:`dummygrad_b200.parallel.tp`). The
+modules mirror the reference's block structure (src/attention.h:49-114, src/transformer.h:11-66)
+with the weights cut Megatron-style: Q/K/V and fc1 by columns (heads / hidden units), the
+attention out-projection and fc2 by rows. LayerNorm, biases of row-parallel layers and the
+embeddings are replicated; their gradients come from different token shards on every rank and
+are summed over the tensor-parallel group after backward (``allreduce_replicated_grads``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib as L
+from .. import init
+from ..models.layers import LayerNorm, Module
+from ..ops import functional as F
+from ..ops import kernels as K
+from ..tensor import Node, Tensor
+from . import tp
+
+
+def _mark_replicated(*tensors):
+    for t in tensors:
+        t.name = "tp_replicated"
+
+
+class ColumnParallelBackward(Node):
+    """Backward of Y = gather(x) W (+ b) for one weight: dx through the fused GEMM->reduce-scatter."""
+
+    def __init__(self, ctx, x_full, w, has_bias, key, act_pre=None):
+        super().__init__()
+        self.ctx, self.x_full, self.w, self.has_bias, self.key, self.act_pre = ctx, x_full, w, has_bias, key, act_pre
+
+    def apply(self, grads):
+        g = K.contiguous(grads[0])
+        if self.act_pre is not None:
+            g = K.ew("GELU_BWD", g, self.act_pre)
+        n = self.w.shape[1]
+        dW = K.gemm2d(self.x_full, g, trans_a=True)
+        dx = tp.gemm_rs(self.ctx, g, self.w, trans_w=True, key=("bwd", self.key))
+        res = [dx, dW]
+        if self.has_bias:
+            db, _ = K.reduce_cols(g.reshape(1, g.shape[0], n), L.RED_SUM)
+            res.append(db.reshape(1, n))
+        return res
+
+    def release_variables(self):
+        self.x_full = self.act_pre = None
+
+
+def column_parallel(ctx: tp.TPContext, x: Tensor, W: Tensor, b: Tensor | None, key, act: str | None = None):
+    """x [T/W, K] token shard -> act(gather(x) @ W + b) [T, N_local]. Returns (out, gathered x)."""
+    xd = K.contiguous(x.data)
+    bd = K.contiguous(b.data).reshape(-1) if b is not None else None
+    y, x_full = tp.ag_gemm(ctx, xd, K.contiguous(W.data), bd, key=("fwd", key))
+    pre = None
+    if act == "gelu":
+        pre = y
+        y = K.ew("GELU", pre)
+    inputs = [x, W] + ([b] if b is not None else [])
+    out = F._result(y, lambda: ColumnParallelBackward(ctx, x_full, K.contiguous(W.data), b is not None, key, pre),
+                    inputs)
+    return out, x_full
+
+
+class GatheredLinearBackward(Node):
+    """Backward of Y = X_full W (+ b) where X_full is an already gathered activation that another
+    column-parallel op of the same input produced: contributes dW, db and a partial dX that the
+    caller's fused reduce-scatter does not cover, so it is scattered with the collective here."""
+
+    def __init__(self, ctx, x_full, w, has_bias, key):
+        super().__init__()
+        self.ctx, self.x_full, self.w, self.has_bias, self.key = ctx, x_full, w, has_bias, key
+
+    def apply(self, grads):
+        g = K.contiguous(grads[0])
+        n = self.w.shape[1]
+        dW = K.gemm2d(self.x_full, g, trans_a=True)
+        dx = tp.gemm_rs(self.ctx, g, self.w, trans_w=True, key=("bwd", self.key))
+        res = [dx, dW]
+        if self.has_bias:
+            db, _ = K.reduce_cols(g.reshape(1, g.shape[0], n), L.RED_SUM)
+            res.append(db.reshape(1, n))
+        return res
+
+    def release_variables(self):
+        self.x_full = None
+
+
+def gathered_linear(ctx, x: Tensor, x_full: torch.Tensor, W: Tensor, b: Tensor | None, key) -> Tensor:
+    """gather(x) @ W + b using the gathered copy ``x_full`` that a sibling column_parallel left."""
+    bd = K.contiguous(b.data).reshape(-1) if b is not None else None
+    y = K.gemm2d(x_full, K.contiguous(W.data), bias=bd)
+    inputs = [x, W] + ([b] if b is not None else [])
+    return F._result(y, lambda: GatheredLinearBackward(ctx, x_full, K.contiguous(W.data), b is not None, key), inputs)
+
+
+class RowParallelBackward(Node):
+    def __init__(self, ctx, x, w, has_bias, has_res, key):
+        super().__init__()
+        self.ctx, self.x, self.w, self.has_bias, self.has_res, self.key = ctx, x, w, has_bias, has_res, key
+
+    def apply(self, grads):
+        g = K.contiguous(grads[0])                       # [T/W, N] token shard
+        # dX = gather(dy) W^T through the fused all-gather->GEMM; the gathered dy stays in the buffer
+        dX, g_full = tp.ag_gemm(self.ctx, g, self.w, trans_w=True, key=("bwd", self.key))
+        dW = K.gemm2d(self.x, g_full, trans_a=True)
+        res = [dX, dW]
+        if self.has_bias:
+            db, _ = K.reduce_cols(g_full.reshape(1, g_full.shape[0], g_full.shape[1]), L.RED_SUM)
+            res.append(db.reshape(1, -1))
+        if self.has_res:
+            res.append(g)
+        return res
+
+    def release_variables(self):
+        self.x = None
+
+
+def row_parallel(ctx: tp.TPContext, x: Tensor, W: Tensor, b: Tensor | None, residual: Tensor | None, key) -> Tensor:
+    """x [T, K_local] -> scatter_rows(sum_ranks x @ W) + b + residual  [T/W, N]."""
+    xd, wd = K.contiguous(x.data), K.contiguous(W.data)
+    bd = K.contiguous(b.data).reshape(-1) if b is not None else None
+    rd = K.contiguous(residual.data) if residual is not None else None
+    y = tp.gemm_rs(ctx, xd, wd, bd, rd, key=("fwd", key))
+    inputs = [x, W] + ([b] if b is not None else []) + ([residual] if residual is not None else [])
+    return F._result(y, lambda: RowParallelBackward(ctx, xd, wd, b is not None, residual is not None, key), inputs)
+
+
+_LAYER_IDS = [0]
+
+
+def _next_id() -> int:
+    _LAYER_IDS[0] += 1
+    return _LAYER_IDS[0]
+
+
+class TPAttention(Module):
+    """Multi-head attention with heads sharded over the tensor-parallel group. Input and output are
+    token shards [T/W, d]; q/k/v are column-parallel (one all-gather feeds all three), the
+    out-projection is row-parallel with the residual add in its epilogue."""
+
+    def __init__(self, ctx: tp.TPContext, d_model: int, n_heads: int, batch_seq: tuple[int, int], causal=True,
+                 dtype=None, device=None):
+        W = ctx.world
+        assert n_heads % W == 0 and d_model % n_heads == 0
+        self.ctx, self.d_model, self.n_heads, self.h_local = ctx, d_model, n_heads, n_heads // W
+        self.d_k = d_model // n_heads
+        dl = d_model // W
+        self.dl = dl
+        self.Wq = init.kaiming([d_model, dl], dtype=dtype, device=device)
+        self.Wk = init.kaiming([d_model, dl], dtype=dtype, device=device)
+        self.Wv = init.kaiming([d_model, dl], dtype=dtype, device=device)
+        self.bq, self.bk, self.bv = (Tensor([1, dl], True, dtype=dtype, device=device) for _ in range(3))
+        self.Wo = init.kaiming([dl, d_model], dtype=dtype, device=device)
+        # kaiming uses fan_in = rows of the shard; keep the scale of the full [d, d] matrix
+        from ..models.layers import scale_
+        scale_(self.Wo, math.sqrt(dl / d_model))
+        self.bo = Tensor([1, d_model], True, dtype=dtype, device=device)
+        self.bo.name = "tp_identical"
+        self.causal = causal
+        self.id = _next_id()
+        self.batch_seq = batch_seq
+
+    def forward(self, x: Tensor, residual: Tensor | None = None, batch_seq=None) -> Tensor:
+        B, S = batch_seq or self.batch_seq
+        ctx = self.ctx
+        q, x_full = column_parallel(ctx, x, self.Wq, self.bq, key=(self.id, "q"))
+        k = gathered_linear(ctx, x, x_full, self.Wk, self.bk, key=(self.id, "k"))
+        v = gathered_linear(ctx, x, x_full, self.Wv, self.bv, key=(self.id, "v"))
+        q3, k3, v3 = (F.reshape(t, [B, S, self.dl]) for t in (q, k, v))
+        o = F.mha_core(q3, k3, v3, self.h_local, causal=self.causal, scale=1.0 / math.sqrt(self.d_k))
+        return row_parallel(ctx, F.reshape(o, [B * S, self.dl]), self.Wo, self.bo, residual, key=(self.id, "o"))
+
+    def parameters(self):
+        return [self.Wq, self.bq, self.Wk, self.bk, self.Wv, self.bv, self.Wo, self.bo]
+
+
+class TPFeedForward(Module):
+    def __init__(self, ctx: tp.TPContext, d_model: int, d_ff: int, dtype=None, device=None):
+        W = ctx.world
+        assert d_ff % W == 0
+        self.ctx = ctx
+        fl = d_ff // W
+        self.W1 = init.kaiming([d_model, fl], dtype=dtype, device=device)
+        self.b1 = Tensor([1, fl], True, dtype=dtype, device=device)
+        self.W2 = init.kaiming([fl, d_model], dtype=dtype, device=device)
+        from ..models.layers import scale_
+        scale_(self.W2, math.sqrt(fl / d_ff))
+        self.b2 = Tensor([1, d_model], True, dtype=dtype, device=device)
+        self.b2.name = "tp_identical"
+        self.id = _next_id()
+
+    def forward(self, x: Tensor, residual: Tensor | None = None) -> Tensor:
+        h, _ = column_parallel(self.ctx, x, self.W1, self.b1, key=(self.id, "1"), act="gelu")
+        return row_parallel(self.ctx, h, self.W2, self.b2, residual, key=(self.id, "2"))
+
+    def parameters(self):
+        return [self.W1, self.b1, self.W2, self.b2]
+
+
+class TPBlock(Module):
+    """Pre-LN block on token shards: x1 = x + attn(ln1(x)); out = x1 + ffn(ln2(x1))."""
+
+    def __init__(self, ctx, d_model, n_heads, d_ff, batch_seq, dtype=None, device=None):
+        self.ln1 = LayerNorm(d_model, dtype=dtype, device=device)
+        self.attn = TPAttention(ctx, d_model, n_heads, batch_seq, True, dtype=dtype, device=device)
+        self.ln2 = LayerNorm(d_model, dtype=dtype, device=device)
+        self.ffn = TPFeedForward(ctx, d_model, d_ff, dtype=dtype, device=device)
+        _mark_replicated(self.ln1.gamma, self.ln1.beta, self.ln2.gamma, self.ln2.beta)
+
+    def forward(self, x: Tensor, batch_seq=None) -> Tensor:
+        x1 = self.attn.forward(self.ln1.forward(x), residual=x, batch_seq=batch_seq)
+        return self.ffn.forward(self.ln2.forward(x1), residual=x1)
+
+    def parameters(self):
+        return self.ln1.parameters() + self.attn.parameters() + self.ln2.parameters() + self.ffn.parameters()
+
+
+class TPGPT(Module):
+    """GPT decoder with tensor-parallel blocks and sequence-parallel everything else. Embeddings,
+    LayerNorms and the weight-tied head are replicated and work on this rank's token shard."""
+
+    def __init__(self, ctx: tp.TPContext, vocab_size, max_seq_len, d_model, n_heads, n_layers, d_ff, batch_seq,
+                 dtype=None, device=None):
+        from ..models.layers import Embedding, scale_
+        self.ctx = ctx
+        self.token_emb = Embedding(vocab_size, d_model, dtype=dtype, device=device)
+        self.pos_emb = Embedding(max_seq_len, d_model, dtype=dtype, device=device)
+        self.blocks = []
+        s = 1.0 / math.sqrt(2.0 * n_layers)
+        for _ in range(n_layers):
+            blk = TPBlock(ctx, d_model, n_heads, d_ff, batch_seq, dtype=dtype, device=device)
+            scale_(blk.attn.Wo, s)
+            scale_(blk.ffn.W2, s)
+            self.blocks.append(blk)
+        self.ln_f = LayerNorm(d_model, dtype=dtype, device=device)
+        _mark_replicated(self.token_emb.weight, self.pos_emb.weight, self.ln_f.gamma, self.ln_f.beta)
+        self.vocab_size, self.d_model, self.batch_seq = vocab_size, d_model, batch_seq
+
+    def loss(self, ids: torch.Tensor, targets: torch.Tensor) -> Tensor:
+        """ids [B, S], targets [B*S] (whole micro-batch, same on every rank of the group). Returns this
+        rank's share of the mean loss; the global loss is the SUM over the ranks of the group."""
+        B, S = ids.shape
+        W, r = self.ctx.world, self.ctx.rank
+        T = B * S
+        rows = T // W
+        flat = ids.reshape(-1)
+        my_ids = flat[r * rows:(r + 1) * rows]
+        pos = (torch.arange(T, device=ids.device, dtype=torch.int64) % S)[r * rows:(r + 1) * rows]
+        x = F.embedding(self.token_emb.weight, my_ids, self.pos_emb.weight, pos)
+        for blk in self.blocks:
+            x = blk.forward(x, batch_seq=(B, S))
+        x = self.ln_f.forward(x)
+        logits = F.matmul(x, F.transpose(self.token_emb.weight, 0, 1))
+        loss = F.softmax_cross_entropy(logits, targets[r * rows:(r + 1) * rows], inplace_grad=True)
+        # every rank averages over its own T/W tokens; scaled by 1/W the per-rank values ADD UP to the
+        # mean over all tokens, and so do the gradients that the collectives and the replicated-
+        # parameter all-reduce combine
+        return F.mul_scalar(loss, 1.0 / W) if W > 1 else loss
+
+    def parameters(self):
+        p = self.token_emb.parameters() + self.pos_emb.parameters()
+        for blk in self.blocks:
+            p += blk.parameters()
+        return p + self.ln_f.parameters()
+
+
+def allreduce_replicated_grads(params, ctx: tp.TPContext, dp_group=None, dp_world: int = 1) -> None:
+    """Sum the gradients of replicated parameters over the tensor-parallel group (each rank saw a
+    different token shard) and average every gradient over the data-parallel group."""
+    for p in params:
+        if p.grad is None:
+            continue
+        g = p.grad.data
+        if ctx.world > 1 and p.name == "tp_replicated":
+            if g.is_cuda or g.dtype != torch.bfloat16:
+                dist.all_reduce(g, group=ctx.group)
+            else:
+                gf = g.float()
+                dist.all_reduce(gf, group=ctx.group)
+                g.copy_(gf.to(g.dtype))
+        if dp_world > 1:
+            if g.is_cuda or g.dtype != torch.bfloat16:
+                dist.all_reduce(g, group=dp_group)
+            else:
+                gf = g.float()
+                dist.all_reduce(gf, group=dp_group)
+                g.copy_(gf.to(g.dtype))

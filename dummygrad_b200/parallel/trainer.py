@@ -67,3 +67,66 @@ class Trainer:
         code = self.dp.check_status() | (K.gemm_status() if self.device.type == "cuda" else 0)
         if code:
             raise RuntimeError(f"device-side wait timed out (status 0x{code:x}); a peer did not signal in time")
+
+
+class TPTrainer:
+    """Training loop for tensor parallelism (optionally x data parallelism).
+
+    Ranks are grouped as ``dp`` replicas of ``tp`` consecutive ranks. Every rank of a tensor-
+    parallel group receives the same micro-batch; activations between the parallel regions are
+    sharded on tokens and the collectives run inside the GEMM kernels. After backward the
+    gradients of replicated parameters are summed over the tensor-parallel group, all gradients are
+    averaged over the data-parallel group (NCCL), and a multi-tensor AdamW updates local weights.
+    """
+
+    def __init__(self, preset: str, *, tp_size: int, micro_batch: int, seq_len: int, lr: float = 2e-4,
+                 weight_decay: float = 0.1, comm: str = "fused", dtype=torch.bfloat16, device=None):
+        import torch.distributed as dist
+        from ..models.gpt import PRESETS
+        from ..optim import AdamW
+        from . import tp as tpm
+        from .tp_layers import TPGPT
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        assert world % tp_size == 0
+        self.tp_size, self.dp_size = tp_size, world // tp_size
+        self.tp_group = self.dp_group = None
+        if world > 1 and tp_size < world:
+            for g in range(self.dp_size):
+                grp = dist.new_group(list(range(g * tp_size, (g + 1) * tp_size)))
+                if rank // tp_size == g:
+                    self.tp_group = grp
+            for t in range(tp_size):
+                grp = dist.new_group(list(range(t, world, tp_size)))
+                if rank % tp_size == t:
+                    self.dp_group = grp
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.ctx = tpm.TPContext(group=self.tp_group, comm=comm, device=self.device, single=(tp_size == 1))
+        v, s, d, h, l, ff = PRESETS[preset]
+        self.model = TPGPT(self.ctx, v, s, d, h, l, ff, (micro_batch, seq_len), dtype=dtype, device=self.device)
+        self.opt = AdamW(self.model.parameters(), lr=lr, weight_decay=weight_decay, beta2=0.95)
+        self.micro_batch = micro_batch
+        self.dp_rank = rank // tp_size
+
+    def step_device(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """ids [B_replica, S] / targets [B_replica * S]: this data-parallel replica's batch, identical on
+        the ranks of its tensor-parallel group. Returns this rank's share of the replica's mean loss."""
+        from .tp_layers import allreduce_replicated_grads
+        B, S = ids.shape
+        mb = min(self.micro_batch, B)
+        n_micro = B // mb
+        self.opt.zero_grad()
+        total = None
+        for i in range(n_micro):
+            loss = self.model.loss(ids[i * mb:(i + 1) * mb], targets[i * mb * S:(i + 1) * mb * S])
+            loss.backward()
+            l = loss.data.reshape(1)
+            total = l if total is None else K.ew("ADD", total, l)
+        allreduce_replicated_grads(self.model.parameters(), self.ctx, self.dp_group, self.dp_size)
+        self.opt.step(grad_scale=1.0 / (n_micro * self.dp_size))
+        return K.ew("MUL_S", total, s0=1.0 / n_micro) if n_micro > 1 else total
+
+    def check(self) -> None:
+        code = self.ctx.check_status() | K.gemm_status()
+        if code:
+            raise RuntimeError(f"device-side wait timed out (status 0x{code:x})")

@@ -1,0 +1,99 @@
+"""T5: tensor-parallel + sequence-parallel logic on CPU ranks (gloo, collective path): a 2-rank
+TP model built from slices of a 1-rank model's weights must give the same loss and gradients."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import dummygrad_b200 as dg
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    dg.set_default_device("cpu")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dummygrad_b200.parallel import tp
+    from dummygrad_b200.parallel.tp_layers import TPGPT, allreduce_replicated_grads
+    dev = torch.device("cpu")
+    V, S, d, H, Lyr, ff, B = 48, 8, 16, 4, 2, 32, 4
+    torch.manual_seed(0)
+    ids = torch.randint(0, V, (B, S))
+    tgt = torch.randint(0, V, (B * S,))
+    # reference: the same architecture on one rank
+    dg.manual_seed(5)
+    ctx1 = tp.TPContext(device=dev, single=True)
+    ref = TPGPT(ctx1, V, S, d, H, Lyr, ff, (B, S), device=dev)
+    lref = ref.loss(ids, tgt)
+    lref.backward()
+    # sharded model whose weights are slices of the reference
+    ctx = tp.TPContext(device=dev, comm="collective")
+    dg.manual_seed(99)
+    m = TPGPT(ctx, V, S, d, H, Lyr, ff, (B, S), device=dev)
+    dl, fl = d // world, ff // world
+    cs = slice(rank * dl, (rank + 1) * dl)
+    fs = slice(rank * fl, (rank + 1) * fl)
+
+    def copy_(dst, src):
+        dst.data.copy_(src)
+
+    pairs = []   # (sharded param, function extracting the matching slice from a full tensor)
+    for name in ("token_emb", "pos_emb"):
+        copy_(getattr(m, name).weight, getattr(ref, name).weight.data)
+        pairs.append((getattr(m, name).weight, getattr(ref, name).weight, lambda t: t))
+    for bm, br in zip(m.blocks, ref.blocks):
+        for a in ("Wq", "Wk", "Wv"):
+            copy_(getattr(bm.attn, a), getattr(br.attn, a).data[:, cs]); pairs.append((getattr(bm.attn, a), getattr(br.attn, a), lambda t: t[:, cs]))
+        for a in ("bq", "bk", "bv"):
+            copy_(getattr(bm.attn, a), getattr(br.attn, a).data[:, cs]); pairs.append((getattr(bm.attn, a), getattr(br.attn, a), lambda t: t[:, cs]))
+        copy_(bm.attn.Wo, br.attn.Wo.data[cs, :]); pairs.append((bm.attn.Wo, br.attn.Wo, lambda t: t[cs, :]))
+        copy_(bm.attn.bo, br.attn.bo.data); pairs.append((bm.attn.bo, br.attn.bo, lambda t: t))
+        copy_(bm.ffn.W1, br.ffn.W1.data[:, fs]); pairs.append((bm.ffn.W1, br.ffn.W1, lambda t: t[:, fs]))
+        copy_(bm.ffn.b1, br.ffn.b1.data[:, fs]); pairs.append((bm.ffn.b1, br.ffn.b1, lambda t: t[:, fs]))
+        copy_(bm.ffn.W2, br.ffn.W2.data[fs, :]); pairs.append((bm.ffn.W2, br.ffn.W2, lambda t: t[fs, :]))
+        copy_(bm.ffn.b2, br.ffn.b2.data); pairs.append((bm.ffn.b2, br.ffn.b2, lambda t: t))
+        for ln in ("ln1", "ln2"):
+            for g in ("gamma", "beta"):
+                copy_(getattr(getattr(bm, ln), g), getattr(getattr(br, ln), g).data)
+                pairs.append((getattr(getattr(bm, ln), g), getattr(getattr(br, ln), g), lambda t: t))
+    for g in ("gamma", "beta"):
+        copy_(getattr(m.ln_f, g), getattr(ref.ln_f, g).data); pairs.append((getattr(m.ln_f, g), getattr(ref.ln_f, g), lambda t: t))
+    loss = m.loss(ids, tgt)
+    loss.backward()
+    allreduce_replicated_grads(m.parameters(), ctx)
+    total = torch.tensor([loss.item()])
+    dist.all_reduce(total)
+    errs = [abs(total.item() - lref.item())]
+    for p, pr, sl in pairs:
+        assert p.grad is not None and pr.grad is not None
+        errs.append((p.grad.data - sl(pr.grad.data)).abs().max().item())
+    if rank == 0:
+        out.put(max(errs))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_tp_two_ranks_match_one_rank():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert err < 2e-4, f"max abs deviation {err}"
