@@ -1,0 +1,295 @@
+// Initialisers, optimizers and NN modules with the reference's names, constructor signatures,
+// parameter shapes and parameters() order (reference: src/init.h, src/optimizers.h, src/linear.h,
+// src/layernorm.h, src/embedding.h, src/attention.h, src/transformer.h), on device kernels.
+#pragma once
+#include <random>
+#include "dg_ops3.h"
+
+// ------------------------------------------------------------------ init (src/init.h)
+// The global generator keeps the reference's type and seeding API. Weights are drawn on the host
+// from it (construction order = draw order, as in the reference) and uploaded on first device use.
+inline std::mt19937 g_gen(std::random_device{}());
+inline void manual_seed(unsigned int seed) { g_gen.seed(seed); }
+
+namespace dgshim {
+inline TP normal_tensor(const std::vector<int>& shape, float stddev) {
+  auto t = std::make_shared<Tensor>(shape, true);
+  std::normal_distribution<float> dis(0.0f, stddev);
+  float* p = t->data_ptr();
+  for (int i = 0; i < t->size(); ++i) p[i] = dis(g_gen);
+  return t;
+}
+}  // namespace dgshim
+
+inline std::shared_ptr<Tensor> randn(std::vector<int> shape) { return dgshim::normal_tensor(shape, 1.0f); }
+// N(0, sqrt(1/shape[0])), 2-D only: the reference's definition of "xavier" (src/init.h:23-35)
+inline std::shared_ptr<Tensor> xavier(std::vector<int> shape) {
+  if (shape.size() != 2) throw std::runtime_error("xavier: 2-D shapes only");
+  return dgshim::normal_tensor(shape, std::sqrt(1.0f / (float)shape[0]));
+}
+// N(0, sqrt(2/shape[0])), 2-D only (src/init.h:38-50)
+inline std::shared_ptr<Tensor> kaiming(std::vector<int> shape) {
+  if (shape.size() != 2) throw std::runtime_error("kaiming: 2-D shapes only");
+  return dgshim::normal_tensor(shape, std::sqrt(2.0f / (float)shape[0]));
+}
+inline std::shared_ptr<Tensor> zeros(std::vector<int> shape) { return std::make_shared<Tensor>(shape, false); }
+inline std::shared_ptr<Tensor> ones(std::vector<int> shape) {
+  auto t = std::make_shared<Tensor>(shape, false);
+  dgshim::check(dg_fill(0, t->dev_rw(), t->size(), 1.0f, dgshim::stream()), "fill");
+  return t;
+}
+// Float-encoded indices -> [n, classes] one-hot rows, bounds-checked, no grad (src/init.h:53-65)
+inline std::shared_ptr<Tensor> one_hot(const std::shared_ptr<Tensor>& indices, int num_classes) {
+  using namespace dgshim;
+  auto ic = contiguous(indices);
+  const int n = ic->size();
+  DevBuf idx((size_t)n * sizeof(int64_t)), bad(sizeof(int), true);
+  check(dg_index_from_float((int64_t*)idx.p, ic->dev_ro(), n, num_classes, (int*)bad.p, stream()), "index conversion");
+  int h_bad = 0;
+  check(dg_rt_d2h(&h_bad, bad.p, sizeof(int), stream()), "status read");
+  if (h_bad) throw std::runtime_error("one_hot: index out of range");
+  auto out = std::make_shared<Tensor>(std::vector<int>{n, num_classes}, false);
+  check(dg_one_hot(out->dev_rw(), (const int64_t*)idx.p, n, num_classes, stream()), "one_hot");
+  return out;
+}
+
+// ------------------------------------------------------------------ optimizers (src/optimizers.h)
+// p -= lr * grad; no-op without a gradient
+inline void SGD(const std::shared_ptr<Tensor>& param, const float& lr) {
+  using namespace dgshim;
+  if (!param || !param->grad) return;
+  auto g = contiguous(param->grad);
+  if (param->is_contiguous() && param->offset == 0) {
+    check(dg_sgd_step(0, param->dev_rw(), nullptr, 0, g->dev_ro(), param->size(), lr, 1.0f, stream()), "sgd");
+  } else {
+    auto c = contiguous(param);
+    auto upd = ew(EW_FMA_S, c->shape, c, g, nullptr, nullptr, BC_SAME, BC_SAME, BC_SAME, 1.0f, -lr);
+    std::vector<int64_t> sh(param->shape.begin(), param->shape.end()), ds(param->strides.begin(), param->strides.end());
+    auto ss_i = make_strides(param->shape);
+    std::vector<int64_t> ss(ss_i.begin(), ss_i.end());
+    check(dg_strided_copy(0, param->dev_rw(), ds.data(), upd->dev_ro(), ss.data(), sh.data(), (int)sh.size(), stream()),
+          "strided copy");
+  }
+}
+
+// Per-parameter Adam state; the moments live on the device (reference keeps host vectors, src/optimizers.h:17-22)
+struct ParamState {
+  std::shared_ptr<dgshim::DevBuf> m, v;
+  int t = 0;
+};
+
+class Adam {
+ public:
+  std::unordered_map<Tensor*, ParamState> state;
+  float lr, b1, b2, E;
+  Adam(float lr = 0.001f, float b1 = 0.9f, float b2 = 0.999f, float E = 1e-8f) : lr(lr), b1(b1), b2(b2), E(E) {}
+
+  // Same update as the reference (src/optimizers.h:32-59): per-tensor step counter, bias correction,
+  // p -= lr * mhat / (sqrt(vhat) + E), no weight decay.
+  void step(const std::shared_ptr<Tensor>& param) {
+    using namespace dgshim;
+    if (!param || !param->grad) return;
+    if (!param->is_contiguous()) throw std::runtime_error("Adam::step: parameter must be contiguous");
+    const int size = param->size();
+    auto& ps = state[param.get()];
+    if (!ps.m) {
+      ps.m = std::make_shared<DevBuf>((size_t)size * sizeof(float), true);
+      ps.v = std::make_shared<DevBuf>((size_t)size * sizeof(float), true);
+    }
+    ps.t++;
+    auto g = contiguous(param->grad);
+    check(dg_adam_step(0, param->dev_rw(), nullptr, 0, g->dev_ro(), (float*)ps.m->p, (float*)ps.v->p, size, lr, b1, b2, E,
+                       0.0f, ps.t, 1.0f, stream()), "adam");
+  }
+};
+
+// ------------------------------------------------------------------ modules
+class Linear {
+ public:
+  std::shared_ptr<Tensor> W, b;
+  Linear(int fan_in, int fan_out, float bias = 0.0f) {
+    W = kaiming({fan_in, fan_out});
+    b = std::make_shared<Tensor>(std::vector<int>{1, fan_out});
+    if (bias != 0.0f) {
+      float* p = b->data_ptr();
+      for (int i = 0; i < b->size(); ++i) p[i] = bias;
+    }
+  }
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x) { return cast_n_add(matmul(x, W), b); }
+  std::vector<std::shared_ptr<Tensor>> parameters() const { return {W, b}; }
+};
+
+class LayerNorm {
+ public:
+  std::shared_ptr<Tensor> gamma, beta;
+  float eps;
+  LayerNorm(int features, float eps = 1e-5f) : eps(eps) {
+    gamma = std::make_shared<Tensor>(std::vector<int>{1, features});
+    beta = std::make_shared<Tensor>(std::vector<int>{1, features});
+    float* g = gamma->data_ptr();
+    for (int i = 0; i < features; ++i) g[i] = 1.0f;
+  }
+  // The reference's seven-op composition (src/layernorm.h:29-39): biased variance, eps inside the sqrt.
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x) {
+    auto mu = mean(x, 1);
+    auto xmu = cast_n_sub(x, mu);
+    auto variance = var(x, 1);
+    auto sd = sqrt(add_scalar(variance, eps));
+    auto x_norm = cast_n_div(xmu, sd);
+    return scale_n_shift(x_norm, gamma, beta);
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const { return {gamma, beta}; }
+};
+
+class Embedding {
+ public:
+  std::shared_ptr<Tensor> weight;
+  int num_embeddings, embedding_dim;
+  Embedding(int num_embeddings, int embedding_dim) : num_embeddings(num_embeddings), embedding_dim(embedding_dim) {
+    weight = xavier({num_embeddings, embedding_dim});
+  }
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& indices) {
+    return matmul(one_hot(indices, num_embeddings), weight);
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const { return {weight}; }
+};
+
+namespace dgshim {
+inline std::vector<TP> join(std::initializer_list<std::vector<TP>> lists) {
+  std::vector<TP> out;
+  for (auto& l : lists) out.insert(out.end(), l.begin(), l.end());
+  return out;
+}
+}  // namespace dgshim
+
+class SelfAttention {
+ public:
+  Linear W_q, W_k, W_v;
+  int d_k;
+  bool causal;
+  SelfAttention(int d_model, bool causal = false)
+      : W_q(d_model, d_model), W_k(d_model, d_model), W_v(d_model, d_model), d_k(d_model), causal(causal) {}
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x) {
+    auto Q = W_q.forward(x), K = W_k.forward(x), V = W_v.forward(x);
+    auto scores = mul_scalar(matmul(Q, transpose(K, -2, -1)), 1.0f / std::sqrt((float)d_k));
+    if (causal) scores = causal_mask(scores);
+    return matmul(softmax(scores), V);
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const {
+    return dgshim::join({W_q.parameters(), W_k.parameters(), W_v.parameters()});
+  }
+};
+
+class MultiHeadAttention {
+ public:
+  Linear W_q, W_k, W_v, W_o;
+  int d_model, n_heads, d_k;
+  bool causal;
+  MultiHeadAttention(int d_model, int n_heads, bool causal = false)
+      : W_q(d_model, d_model), W_k(d_model, d_model), W_v(d_model, d_model), W_o(d_model, d_model), d_model(d_model),
+        n_heads(n_heads), d_k(d_model / n_heads), causal(causal) {}
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x_in) {
+    auto x = x_in;
+    const bool is_2d = x->ndim() == 2;
+    if (is_2d) x = reshape(x, {1, x->shape[0], x->shape[1]});
+    const int B = x->shape[0], S = x->shape[1];
+    auto Q = W_q.forward(x), K = W_k.forward(x), V = W_v.forward(x);
+    auto Qs = transpose(reshape(Q, {B, S, n_heads, d_k}), 1, 2);
+    auto Ks = transpose(reshape(K, {B, S, n_heads, d_k}), 1, 2);
+    auto Vs = transpose(reshape(V, {B, S, n_heads, d_k}), 1, 2);
+    auto scores = mul_scalar(matmul(Qs, transpose(Ks, -2, -1)), 1.0f / std::sqrt((float)d_k));
+    if (causal) scores = causal_mask(scores);
+    auto attn_out = matmul(softmax(scores), Vs);
+    auto merged = reshape(transpose(attn_out, 1, 2), {B, S, d_model});
+    auto out = W_o.forward(merged);
+    if (is_2d) out = reshape(out, {S, d_model});
+    return out;
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const {
+    return dgshim::join({W_q.parameters(), W_k.parameters(), W_v.parameters(), W_o.parameters()});
+  }
+};
+
+class FeedForward {
+ public:
+  Linear fc1, fc2;
+  FeedForward(int d_model, int d_ff = 0)
+      : fc1(d_model, d_ff > 0 ? d_ff : 4 * d_model), fc2(d_ff > 0 ? d_ff : 4 * d_model, d_model) {}
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x) { return fc2.forward(gelu(fc1.forward(x))); }
+  std::vector<std::shared_ptr<Tensor>> parameters() const { return dgshim::join({fc1.parameters(), fc2.parameters()}); }
+};
+
+// Pre-LN block: x1 = x + attn(ln1(x)); out = x1 + ffn(ln2(x1)) (src/transformer.h:34-66)
+class TransformerBlock {
+ public:
+  LayerNorm ln1;
+  MultiHeadAttention attn;
+  LayerNorm ln2;
+  FeedForward ffn;
+  TransformerBlock(int d_model, int n_heads, bool causal = true)
+      : ln1(d_model), attn(d_model, n_heads, causal), ln2(d_model), ffn(d_model) {}
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& x) {
+    auto x1 = add(x, attn.forward(ln1.forward(x)));
+    return add(x1, ffn.forward(ln2.forward(x1)));
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const {
+    return dgshim::join({ln1.parameters(), attn.parameters(), ln2.parameters(), ffn.parameters()});
+  }
+};
+
+// Weight-tied GPT decoder (src/transformer.h:69-144)
+class GPT {
+ public:
+  Embedding token_emb, pos_emb;
+  std::vector<std::shared_ptr<TransformerBlock>> blocks;
+  LayerNorm ln_f;
+  int vocab_size, max_seq_len, d_model;
+  GPT(int vocab_size, int max_seq_len, int d_model, int n_heads, int n_layers)
+      : token_emb(vocab_size, d_model), pos_emb(max_seq_len, d_model), ln_f(d_model), vocab_size(vocab_size),
+        max_seq_len(max_seq_len), d_model(d_model) {
+    const float scale = 1.0f / std::sqrt(2.0f * n_layers);
+    for (int i = 0; i < n_layers; ++i) {
+      blocks.push_back(std::make_shared<TransformerBlock>(d_model, n_heads, true));
+      for (auto& w : {blocks.back()->attn.W_o.W, blocks.back()->ffn.fc2.W}) {
+        float* p = w->data_ptr();
+        for (int j = 0; j < w->size(); ++j) p[j] *= scale;
+      }
+    }
+  }
+  std::shared_ptr<Tensor> forward(const std::shared_ptr<Tensor>& input_ids, const std::shared_ptr<Tensor>& pos_ids) {
+    auto x = add(token_emb.forward(input_ids), pos_emb.forward(pos_ids));
+    for (auto& blk : blocks) x = blk->forward(x);
+    auto x_norm = ln_f.forward(x);
+    return matmul(x_norm, transpose(token_emb.weight, 0, 1));   // tied head
+  }
+  std::vector<std::shared_ptr<Tensor>> parameters() const {
+    auto p = dgshim::join({token_emb.parameters(), pos_emb.parameters()});
+    for (auto& blk : blocks) { auto pb = blk->parameters(); p.insert(p.end(), pb.begin(), pb.end()); }
+    auto pl = ln_f.parameters();
+    p.insert(p.end(), pl.begin(), pl.end());
+    return p;
+  }
+};
+
+// ------------------------------------------------------------------ parameter files
+// Raw little-endian float32, parameters concatenated in parameters() order: the only on-disk
+// convention the reference uses (src/mars.cpp:152-166 reads such a stream).
+#include <fstream>
+inline void save_parameters(const std::string& path, const std::vector<std::shared_ptr<Tensor>>& params) {
+  std::ofstream f(path, std::ios::binary);
+  if (!f) throw std::runtime_error("save_parameters: cannot open " + path);
+  for (auto& p : params) {
+    auto c = dgshim::contiguous(p);
+    f.write(reinterpret_cast<const char*>(c->storage->host_ro() + c->offset), (std::streamsize)c->size() * sizeof(float));
+  }
+}
+inline void load_parameters(const std::string& path, const std::vector<std::shared_ptr<Tensor>>& params) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) throw std::runtime_error("load_parameters: cannot open " + path);
+  for (auto& p : params) {
+    std::vector<float> buf(p->size());
+    f.read(reinterpret_cast<char*>(buf.data()), (std::streamsize)buf.size() * sizeof(float));
+    if (!f) throw std::runtime_error("load_parameters: file too short");
+    p->fill(buf);
+  }
+}

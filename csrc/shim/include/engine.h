@@ -168,3 +168,5 @@ struct Tensor : std::enable_shared_from_this<Tensor> {
 
   void backward(bool retain_graph = false);
 };
+
+#include "dg_engine_impl.h"   // accumulation, leaf sinks and Tensor::backward
