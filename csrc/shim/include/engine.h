@@ -145,24 +145,27 @@ struct Tensor : std::enable_shared_from_this<Tensor> {
   }
   std::shared_ptr<Tensor> transpose(int d0 = -2, int d1 = -1) { return _transpose(d0, d1); }
 
-  // Nested-bracket print, stride-aware (reference: src/engine.h:221-258)
-  void print_rec(const float* base, int dim, int off, std::ostream& os) {
+  // Nested-bracket print, stride-aware; sub-arrays of every non-innermost dim start on a new line
+  // indented by their depth, then ", shape=(a,b)" (same text as reference: src/engine.h:221-258).
+  void print_rec(const float* base, int dim, int off, std::ostream& os) const {
+    const bool inner = dim == ndim() - 1;
     os << "[";
     for (int i = 0; i < shape[dim]; ++i) {
-      if (dim == ndim() - 1) os << base[off + i * strides[dim]];
+      if (i > 0) os << (inner ? ", " : ",\n" + std::string(dim + 1, ' '));
+      if (inner) os << (base ? base[off + i * strides[dim]] : 0.0f);
       else print_rec(base, dim + 1, off + i * strides[dim], os);
-      if (i + 1 < shape[dim]) os << ", ";
     }
     os << "]";
   }
-  void show_shape(std::ostream& os) {
+  void show_shape(std::ostream& os) const {
     os << ", shape=(";
     for (size_t i = 0; i < shape.size(); ++i) os << shape[i] << (i + 1 < shape.size() ? "," : "");
-    os << ")" << std::endl;
+    os << ")\n";
   }
   void show() { print_rec(storage->host_ro() + offset, 0, 0, std::cout); show_shape(std::cout); }
+  // A tensor without a gradient prints zeros in its own shape, as the reference does.
   void show_grad() {
-    if (!grad) { std::cout << "None" << std::endl; return; }
+    if (!grad) { print_rec(nullptr, 0, 0, std::cout); show_shape(std::cout); return; }
     grad->show();
   }
 

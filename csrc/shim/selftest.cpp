@@ -1,0 +1,201 @@
+// Self-test of the C++ shim: every op family is run on the device and compared with a host
+// computation written here; a small GPT forward is then walked stage by stage. Prints one line per
+// check and exits non-zero if any check fails.
+#include <cmath>
+#include <cstdio>
+#include <functional>
+#include "dummy.h"
+
+static int g_fail = 0;
+using T = std::shared_ptr<Tensor>;
+
+static T make(const std::vector<int>& shape, const std::function<float(int)>& f, bool grad = true) {
+  auto t = std::make_shared<Tensor>(shape, grad);
+  std::vector<float> v(t->size());
+  for (int i = 0; i < (int)v.size(); ++i) v[i] = f(i);
+  t->fill(v);
+  return t;
+}
+
+static void expect(const char* name, const T& got, const std::vector<float>& want, float tol = 1e-4f) {
+  auto c = dgshim::contiguous(got);
+  float worst = 0.0f;
+  bool bad = (int)want.size() != c->size();
+  for (int i = 0; !bad && i < c->size(); ++i) {
+    float g = c->data_at(i);
+    if (std::isnan(g)) { bad = true; break; }
+    worst = std::max(worst, std::fabs(g - want[i]) / (1.0f + std::fabs(want[i])));
+  }
+  bad = bad || worst > tol;
+  std::printf("[%s] %-28s max rel err %.3g\n", bad ? "FAIL" : "PASS", name, worst);
+  if (bad) ++g_fail;
+}
+
+static void finite(const char* name, const T& t) {
+  auto c = dgshim::contiguous(t);
+  int nan = 0;
+  float lo = 1e30f, hi = -1e30f;
+  for (int i = 0; i < c->size(); ++i) {
+    float g = c->data_at(i);
+    if (std::isnan(g) || std::isinf(g)) ++nan;
+    else { lo = std::min(lo, g); hi = std::max(hi, g); }
+  }
+  std::printf("[%s] %-28s min %.4g max %.4g non-finite %d\n", nan ? "FAIL" : "PASS", name, lo, hi, nan);
+  if (nan) ++g_fail;
+}
+
+int main() {
+  const int R = 4, C = 16;
+  auto f = [](int i) { return std::sin(0.37f * i) + 0.1f * (i % 5); };
+  auto x = make({R, C}, f);
+
+  // ---- reductions with keepdim statistics
+  std::vector<float> mu(R), vr(R), colsum(C, 0.0f);
+  for (int r = 0; r < R; ++r) {
+    float s = 0, q = 0;
+    for (int c = 0; c < C; ++c) { s += f(r * C + c); colsum[c] += f(r * C + c); }
+    mu[r] = s / C;
+    for (int c = 0; c < C; ++c) q += (f(r * C + c) - mu[r]) * (f(r * C + c) - mu[r]);
+    vr[r] = q / C;
+  }
+  expect("mean(x,1)", mean(x, 1), mu);
+  expect("var(x,1)", var(x, 1), vr);
+  expect("sum(x,0)", sum(x, 0), colsum);
+  {
+    std::vector<float> sd(R);
+    for (int r = 0; r < R; ++r) sd[r] = std::sqrt(vr[r]);
+    expect("std_dev(x,1)", std_dev(x, 1), sd);
+  }
+
+  // ---- cast ops and layer norm
+  std::vector<float> xn(R * C);
+  for (int r = 0; r < R; ++r)
+    for (int c = 0; c < C; ++c) xn[r * C + c] = (f(r * C + c) - mu[r]) / std::sqrt(vr[r] + 1e-5f);
+  {
+    auto m = mean(x, 1);
+    std::vector<float> d(R * C);
+    for (int i = 0; i < R * C; ++i) d[i] = f(i) - mu[i / C];
+    expect("cast_n_sub(x,mean)", cast_n_sub(x, m), d);
+    auto sd = sqrt(add_scalar(var(x, 1), 1e-5f));
+    expect("cast_n_div(xmu,sd)", cast_n_div(cast_n_sub(x, m), sd), xn);
+  }
+  LayerNorm ln(C);
+  expect("LayerNorm.forward", ln.forward(x), xn);
+
+  // ---- softmax / masks / losses
+  std::vector<float> sm(R * C);
+  for (int r = 0; r < R; ++r) {
+    float mx = -1e30f, s = 0;
+    for (int c = 0; c < C; ++c) mx = std::max(mx, f(r * C + c));
+    for (int c = 0; c < C; ++c) s += std::exp(f(r * C + c) - mx);
+    for (int c = 0; c < C; ++c) sm[r * C + c] = std::exp(f(r * C + c) - mx) / s;
+  }
+  auto probs = softmax(x);
+  expect("softmax", probs, sm);
+  {
+    auto tgt = make({R, C}, [&](int i) { return (i % C) == (i / C) ? 1.0f : 0.0f; }, false);
+    float l = 0;
+    for (int r = 0; r < R; ++r) l -= std::log(sm[r * C + r] + 1e-8f);
+    expect("cross_entropy", cross_entropy(probs, tgt), {l / (R * C)});   // the reference divides by the element count
+  }
+  {
+    auto sq = make({4, 4}, [](int i) { return 0.25f * i; });
+    auto cm = softmax(causal_mask(sq));
+    std::vector<float> want(16, 0.0f);
+    for (int r = 0; r < 4; ++r) {
+      float s = 0;
+      for (int c = 0; c <= r; ++c) s += std::exp(0.25f * (r * 4 + c) - 0.25f * (r * 4 + r));
+      for (int c = 0; c <= r; ++c) want[r * 4 + c] = std::exp(0.25f * (r * 4 + c) - 0.25f * (r * 4 + r)) / s;
+    }
+    expect("softmax(causal_mask)", cm, want);
+  }
+
+  // ---- matmul with a transposed view and a 4-D batch
+  {
+    auto a = make({R, C}, f);
+    auto w = make({8, C}, [](int i) { return 0.01f * (i % 13) - 0.05f; });
+    std::vector<float> want(R * 8, 0.0f);
+    for (int r = 0; r < R; ++r)
+      for (int n = 0; n < 8; ++n)
+        for (int c = 0; c < C; ++c) want[r * 8 + n] += f(r * C + c) * (0.01f * ((n * C + c) % 13) - 0.05f);
+    expect("matmul(a, transpose(w))", matmul(a, transpose(w, 0, 1)), want);
+    auto a4 = transpose(reshape(reshape(a, {1, R, C}), {1, R, 2, 8}), 1, 2);   // [1,2,R,8]
+    auto s = matmul(a4, transpose(a4, -2, -1));                                // [1,2,R,R]
+    std::vector<float> w2(2 * R * R, 0.0f);
+    for (int h = 0; h < 2; ++h)
+      for (int i = 0; i < R; ++i)
+        for (int j = 0; j < R; ++j)
+          for (int d = 0; d < 8; ++d) w2[(h * R + i) * R + j] += f(i * C + h * 8 + d) * f(j * C + h * 8 + d);
+    expect("head-split QK^T", s, w2);
+  }
+
+  // ---- embedding through one_hot
+  {
+    Embedding emb(10, C);
+    auto ids = make({4}, [](int i) { return (float)(2 * i + 1); }, false);
+    auto e = emb.forward(ids);
+    std::vector<float> want(4 * C);
+    for (int i = 0; i < 4; ++i)
+      for (int c = 0; c < C; ++c) want[i * C + c] = emb.weight->data_at((2 * i + 1) * C + c);
+    expect("Embedding.forward", e, want);
+  }
+
+  // ---- GPT forward walked stage by stage over many random initialisations
+  auto ids = make({4}, [](int i) { return (float)(2 * i + 1); }, false);
+  auto pos = make({4}, [](int i) { return (float)i; }, false);
+  auto count_bad = [](const T& t) {
+    auto c = dgshim::contiguous(t);
+    int bad = 0;
+    for (int i = 0; i < c->size(); ++i) if (!std::isfinite(c->data_at(i))) ++bad;
+    return bad;
+  };
+  int bad_seeds = 0;
+  for (unsigned seed = 1; seed <= 40; ++seed) {
+    manual_seed(seed * 2654435761u);
+    GPT m(10, 4, 16, 2, 2);
+    auto h = add(m.token_emb.forward(ids), m.pos_emb.forward(pos));
+    const char* where = count_bad(h) ? "embeddings" : nullptr;
+    for (size_t b = 0; b < m.blocks.size() && !where; ++b) {
+      auto& blk = *m.blocks[b];
+      auto n1 = blk.ln1.forward(h);
+      if (count_bad(n1)) { where = "ln1"; break; }
+      auto at = blk.attn.forward(n1);
+      if (count_bad(at)) { where = "attention"; break; }
+      auto h1 = add(h, at);
+      auto n2 = blk.ln2.forward(h1);
+      if (count_bad(n2)) { where = "ln2"; break; }
+      auto ff = blk.ffn.forward(n2);
+      if (count_bad(ff)) { where = "feed-forward"; break; }
+      h = add(h1, ff);
+    }
+    if (!where && count_bad(m.forward(ids, pos))) where = "logits (whole forward)";
+    if (where) { std::printf("[FAIL] seed %u: first non-finite values in %s\n", seed, where); ++bad_seeds; }
+  }
+  std::printf("[%s] GPT forward, 40 seeds       %d with non-finite values\n", bad_seeds ? "FAIL" : "PASS", bad_seeds);
+  g_fail += bad_seeds;
+
+  manual_seed(7);
+  GPT model(10, 4, 16, 2, 2);
+  auto logits = model.forward(ids, pos);
+  finite("logits", logits);
+  auto tgt = make({4, 10}, [](int i) { return (i % 10) == 2 * (i / 10) + 1 ? 1.0f : 0.0f; }, false);
+  Adam opt(0.001f);
+  auto params = model.parameters();
+  float first = 0, last = 0;
+  for (int step = 0; step < 30; ++step) {
+    for (auto& p : params) p->zero_grad();
+    auto loss = cross_entropy(softmax(model.forward(ids, pos)), tgt);
+    last = loss->data_at(0);
+    if (step == 0) first = last;
+    loss->backward();
+    if (step == 0)
+      for (size_t i = 0; i < params.size(); ++i)
+        if (params[i]->grad) { char nm[32]; std::snprintf(nm, sizeof nm, "grad of parameter %zu", i); finite(nm, params[i]->grad); }
+    for (auto& p : params) opt.step(p);
+  }
+  bool ok = std::isfinite(last) && last < first;
+  std::printf("[%s] GPT training               loss %.4f -> %.4f\n", ok ? "PASS" : "FAIL", first, last);
+  if (!ok) ++g_fail;
+  std::printf("%s (%d failed)\n", g_fail ? "SELFTEST FAILED" : "SELFTEST PASSED", g_fail);
+  return g_fail ? 1 : 0;
+}
