@@ -161,3 +161,186 @@ def _manifest(params: Sequence, shapes: Sequence[Sequence[int]], names: Sequence
             "params": [{"name": n, "shape": [int(s) for s in sh], "dtype": str(p.dtype).replace("torch.", "")}
                        for n, sh, p in zip(names, shapes, params)],
             "rng": _rng_state(), "config": cfg, "extra": extra or {}}
+
+
+# ----------------------------------------------------------------------------- reader
+class CheckpointReader:
+    """Reassembles logical fp32 tensors from the pieces of all rank files (memory-mapped)."""
+
+    def __init__(self, dirpath: str):
+        self.dirpath = dirpath
+        with open(os.path.join(dirpath, "manifest.json")) as f:
+            self.manifest = json.load(f)
+        if self.manifest.get("format") != FORMAT:
+            raise ValueError(f"{dirpath}: not a {FORMAT} checkpoint")
+        self.shapes = [tuple(p["shape"]) for p in self.manifest["params"]]
+        self._pieces: dict[tuple[int, str], list[tuple[dict, np.memmap]]] = {}
+        for fn in sorted(os.listdir(dirpath)):
+            if not (fn.startswith("rank") and fn.endswith(".json")):
+                continue
+            with open(os.path.join(dirpath, fn)) as f:
+                idx = json.load(f)
+            mm = np.memmap(os.path.join(dirpath, idx["file"]), dtype="<f4", mode="r")
+            for pc in idx["pieces"]:
+                self._pieces.setdefault((pc["param"], pc["kind"]), []).append((pc, mm))
+
+    def has(self, param: int, kind: str) -> bool:
+        return (param, kind) in self._pieces
+
+    def full(self, param: int, kind: str) -> torch.Tensor:
+        """The whole logical tensor of one kind ('master', 'm' or 'v') as fp32 on the host."""
+        shape = self.shapes[param]
+        n = int(np.prod(shape))
+        out = np.empty(n, dtype=np.float32)
+        covered = 0
+        for pc, mm in self._pieces.get((param, kind), []):
+            src = mm[pc["offset"] // 4: pc["offset"] // 4 + pc["numel"]]
+            if pc["layout"] == "flat":
+                out[pc["start"]: pc["start"] + pc["numel"]] = src
+            else:  # block [lo, hi) along dim
+                view = out.reshape(shape)
+                sl = [slice(None)] * len(shape)
+                sl[pc["dim"]] = slice(pc["lo"], pc["hi"])
+                blk = list(shape)
+                blk[pc["dim"]] = pc["hi"] - pc["lo"]
+                view[tuple(sl)] = np.asarray(src).reshape(blk)
+            covered += pc["numel"]
+        if covered != n:
+            raise ValueError(f"checkpoint pieces of parameter {param} ({kind}) cover {covered} of {n} elements")
+        return torch.from_numpy(out).view(shape)
+
+
+def export_bin(dirpath: str, out_path: str) -> int:
+    """Write the fp32 master weights of a checkpoint as one raw stream in parameters() order
+    (loadable by the C++ shim's load_parameters and by ``load_parameters`` above)."""
+    rd = CheckpointReader(dirpath)
+    n = 0
+    with open(out_path, "wb") as f:
+        for i in range(len(rd.shapes)):
+            t = rd.full(i, "master")
+            f.write(t.numpy().astype("<f4", copy=False).tobytes())
+            n += t.numel()
+    return n
+
+
+# ----------------------------------------------------------------------------- data-parallel engine
+def _dp_segments(dp):
+    """(param index, start in the flattened parameter, length, position in the owned state) for
+    every part of a parameter that lies in this rank's shard of a bucket."""
+    index_of = {id(p): i for i, p in enumerate(dp.params)}
+    for b in dp.buckets:
+        sn = b.shard_n(dp.world)
+        lo, hi = b.offset + dp.rank * sn, b.offset + (dp.rank + 1) * sn
+        for p in b.params:
+            o, n = dp.flat_offset[id(p)], p.size()
+            s, e = max(lo, o), min(hi, o + n)
+            if s < e:
+                yield index_of[id(p)], s - o, e - s, b.state_off + (s - lo)
+
+
+def save_dp(dirpath: str, dp, *, step: int, config=None, names=None, extra=None, asynchronous: bool = True) -> SaveHandle:
+    """Checkpoint of a DataParallel engine: every rank writes its fp32 master / m / v shards."""
+    pieces = []
+    for pi, start, ln, pos in _dp_segments(dp):
+        for kind, buf in (("master", dp.master), ("m", dp.m), ("v", dp.v)):
+            if buf is not None:
+                pieces.append(({"param": pi, "kind": kind, "layout": "flat", "start": start}, buf[pos:pos + ln]))
+    man = None
+    if dp.rank == 0:
+        man = _manifest(dp.params, [p.data.shape for p in dp.params], names, step, dp.t, config,
+                        {"kind": "dp", "world": dp.world}, extra)
+    return _write_pieces(dirpath, dp.rank, pieces, man, dp.group, asynchronous)
+
+
+def load_dp(dirpath: str, dp) -> dict:
+    """Load into a DataParallel engine of ANY world size: parameters from the masters, and this
+    rank's owned master / moment ranges."""
+    rd = CheckpointReader(dirpath)
+    if len(rd.shapes) != len(dp.params):
+        raise ValueError("checkpoint and model have different parameter counts")
+    segs: dict[int, list] = {}
+    for pi, start, ln, pos in _dp_segments(dp):
+        segs.setdefault(pi, []).append((start, ln, pos))
+    for i, p in enumerate(dp.params):
+        if tuple(p.data.shape) != rd.shapes[i]:
+            raise ValueError(f"parameter {i}: checkpoint shape {rd.shapes[i]} != model shape {tuple(p.data.shape)}")
+        w = rd.full(i, "master")
+        p.data.copy_(w.to(p.data.dtype))
+        mine = segs.get(i, [])
+        if not mine:
+            continue
+        flats = {"master": w.reshape(-1)}
+        for kind in ("m", "v"):
+            if getattr(dp, kind) is not None and rd.has(i, kind):
+                flats[kind] = rd.full(i, kind).reshape(-1)
+        for start, ln, pos in mine:
+            for kind, src in flats.items():
+                getattr(dp, kind)[pos:pos + ln].copy_(src[start:start + ln])
+    dp.t = int(rd.manifest["optimizer_t"])
+    if dist.is_initialized():
+        dist.barrier(dp.group)
+    return rd.manifest
+
+
+# ----------------------------------------------------------------------------- tensor-parallel models
+def save_tp(dirpath: str, model, opt, ctx, *, step: int, dp_rank: int = 0, config=None, extra=None, group=None,
+            asynchronous: bool = True) -> SaveHandle:
+    """Checkpoint of a tensor-parallel model + multi-tensor AdamW. ``model.param_layout()`` gives
+    (name, shard dim or None) per parameter; sharded ones are written by every rank of the first
+    data-parallel replica as blocks, replicated ones by tensor-parallel rank 0 only."""
+    layout = model.param_layout()
+    params = list(model.parameters())
+    pieces, shapes = [], []
+    for i, (p, (name, dim)) in enumerate(zip(params, layout)):
+        shape = list(p.data.shape)
+        if dim is not None:
+            n = shape[dim]
+            shape[dim] = n * ctx.world
+            meta = {"param": i, "layout": "block", "dim": dim, "lo": ctx.rank * n, "hi": (ctx.rank + 1) * n}
+        else:
+            meta = {"param": i, "layout": "flat", "start": 0}
+        shapes.append(shape)
+        if dp_rank != 0 or (dim is None and ctx.rank != 0):
+            continue
+        st = opt.state[i]
+        master = st.master if st.master is not None else p.data
+        for kind, t in (("master", master), ("m", st.m), ("v", st.v)):
+            pieces.append((dict(meta, kind=kind), t))
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    man = None
+    if rank == 0:
+        man = _manifest(params, shapes, [n for n, _ in layout], step, opt.t, config,
+                        {"kind": "tp", "tp": ctx.world}, extra)
+    return _write_pieces(dirpath, rank, pieces, man, group, asynchronous) if pieces else SaveHandle(dirpath, None, man, group)
+
+
+def load_tp(dirpath: str, model, opt, ctx) -> dict:
+    """Load into a tensor-parallel model of ANY tensor-parallel size (also from a data-parallel
+    checkpoint of the same logical model)."""
+    rd = CheckpointReader(dirpath)
+    layout = model.param_layout()
+    params = list(model.parameters())
+    if len(rd.shapes) != len(params):
+        raise ValueError("checkpoint and model have different parameter counts")
+    for i, (p, (_, dim)) in enumerate(zip(params, layout)):
+        st = opt.state[i]
+        for kind in KINDS:
+            if not rd.has(i, kind):
+                continue
+            t = rd.full(i, kind)
+            if dim is not None:
+                n = p.data.shape[dim]
+                t = t.narrow(dim, ctx.rank * n, n)
+            if tuple(t.shape) != tuple(p.data.shape):
+                raise ValueError(f"parameter {i}: checkpoint block {tuple(t.shape)} != model {tuple(p.data.shape)}")
+            if kind == "master":
+                p.data.copy_(t.to(p.data.dtype))
+                if st.master is not None:
+                    st.master.copy_(t)
+            else:
+                getattr(st, kind).copy_(t)
+        st.t = int(rd.manifest["optimizer_t"])
+    opt.t = int(rd.manifest["optimizer_t"])
+    if dist.is_initialized():
+        dist.barrier()
+    return rd.manifest

@@ -74,11 +74,25 @@ class GPT(Module):
         loss = F.cross_entropy(probs, onehot)
         return F.mul_scalar(loss, float(V)) if reduction == "mean" else loss
 
+    def parameter_names(self) -> list[str]:
+        return gpt_parameter_names(len(self.blocks))
+
     def parameters(self) -> list[Tensor]:
         p = self.token_emb.parameters() + self.pos_emb.parameters()
         for blk in self.blocks:
             p += blk.parameters()
         return p + self.ln_f.parameters()
+
+
+def gpt_parameter_names(n_layers: int) -> list[str]:
+    """Names of a GPT's parameters in parameters() order (used by checkpoints)."""
+    out = ["token_emb.weight", "pos_emb.weight"]
+    for i in range(n_layers):
+        b = f"blocks.{i}."
+        out += [b + "ln1.gamma", b + "ln1.beta"]
+        out += [b + f"attn.W_{x}.{y}" for x in "qkvo" for y in "Wb"]
+        out += [b + "ln2.gamma", b + "ln2.beta", b + "ffn.fc1.W", b + "ffn.fc1.b", b + "ffn.fc2.W", b + "ffn.fc2.b"]
+    return out + ["ln_f.gamma", "ln_f.beta"]
 
 
 PRESETS = {

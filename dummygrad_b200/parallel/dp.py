@@ -167,9 +167,11 @@ class DataParallel:
             b = Bucket(bi, off, numel, [params[order[j]] for j in idxs], state_off=state_off)
             state_off += numel // self.world
             self.buckets.append(b)
+        self.flat_offset: dict[int, int] = {}   # id(parameter) -> element offset in the flat buffers
         for j, i in enumerate(order):
             p = params[i]
             n = p.size()
+            self.flat_offset[id(p)] = offs[j]
             view = self.param_flat[offs[j]:offs[j] + n].view(p.data.shape)
             K.strided_copy(view, p.data)
             p.data = view

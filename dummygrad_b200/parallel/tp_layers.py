@@ -271,6 +271,22 @@ class TPGPT(Module):
         return p + self.ln_f.parameters()
 
 
+def _tpgpt_param_layout(self):
+    """(name, tensor-parallel shard dim or None) per parameter, in parameters() order."""
+    out = [("token_emb.weight", None), ("pos_emb.weight", None)]
+    for i, _ in enumerate(self.blocks):
+        b = f"blocks.{i}."
+        out += [(b + "ln1.gamma", None), (b + "ln1.beta", None),
+                (b + "attn.W_q.W", 1), (b + "attn.W_q.b", 1), (b + "attn.W_k.W", 1), (b + "attn.W_k.b", 1),
+                (b + "attn.W_v.W", 1), (b + "attn.W_v.b", 1), (b + "attn.W_o.W", 0), (b + "attn.W_o.b", None),
+                (b + "ln2.gamma", None), (b + "ln2.beta", None),
+                (b + "ffn.fc1.W", 1), (b + "ffn.fc1.b", 1), (b + "ffn.fc2.W", 0), (b + "ffn.fc2.b", None)]
+    return out + [("ln_f.gamma", None), ("ln_f.beta", None)]
+
+
+TPGPT.param_layout = _tpgpt_param_layout
+
+
 def allreduce_replicated_grads(params, ctx: tp.TPContext, dp_group=None, dp_world: int = 1) -> None:
     """Sum the gradients of replicated parameters over the tensor-parallel group (each rank saw a
     different token shard) and average every gradient over the data-parallel group."""

@@ -62,6 +62,19 @@ class Trainer:
             loss = self.step_device(ids_host, targets_host)
         return float(loss.item())
 
+    # ------------------------------------------------------------------ checkpoints
+    def save(self, dirpath: str, *, step: int, config=None, asynchronous: bool = True):
+        """Start a checkpoint of weights + sharded optimizer state; call ``.wait()`` on the returned
+        handle (every rank) before relying on the files."""
+        from .. import checkpoint
+        names = self.model.parameter_names() if hasattr(self.model, "parameter_names") else None
+        return checkpoint.save_dp(dirpath, self.dp, step=step, config=config, names=names, asynchronous=asynchronous)
+
+    def load(self, dirpath: str) -> dict:
+        """Resume from a checkpoint written at any world size; returns its manifest."""
+        from .. import checkpoint
+        return checkpoint.load_dp(dirpath, self.dp)
+
     def check(self) -> None:
         """Raise if a bounded device-side wait expired during the previous steps."""
         code = self.dp.check_status() | (K.gemm_status() if self.device.type == "cuda" else 0)
@@ -100,9 +113,9 @@ class TPTrainer:
                 grp = dist.new_group(list(range(t, world, tp_size)))
                 if rank % tp_size == t:
                     self.dp_group = grp
-        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.ctx = tpm.TPContext(group=self.tp_group, comm=comm, device=self.device, single=(tp_size == 1))
-        v, s, d, h, l, ff = PRESETS[preset]
+        v, s, d, h, l, ff = PRESETS[preset] if isinstance(preset, str) else preset   # or an explicit 6-tuple
         self.model = TPGPT(self.ctx, v, s, d, h, l, ff, (micro_batch, seq_len), dtype=dtype, device=self.device)
         self.opt = AdamW(self.model.parameters(), lr=lr, weight_decay=weight_decay, beta2=0.95)
         self.micro_batch = micro_batch
@@ -125,6 +138,15 @@ class TPTrainer:
         allreduce_replicated_grads(self.model.parameters(), self.ctx, self.dp_group, self.dp_size)
         self.opt.step(grad_scale=1.0 / (n_micro * self.dp_size))
         return K.ew("MUL_S", total, s0=1.0 / n_micro) if n_micro > 1 else total
+
+    def save(self, dirpath: str, *, step: int, config=None, asynchronous: bool = True):
+        from .. import checkpoint
+        return checkpoint.save_tp(dirpath, self.model, self.opt, self.ctx, step=step, dp_rank=self.dp_rank,
+                                  config=config, asynchronous=asynchronous)
+
+    def load(self, dirpath: str) -> dict:
+        from .. import checkpoint
+        return checkpoint.load_tp(dirpath, self.model, self.opt, self.ctx)
 
     def check(self) -> None:
         code = self.ctx.check_status() | K.gemm_status()

@@ -1,0 +1,191 @@
+"""Checkpoint / resume: bitwise-identical continuation, re-sharding across world sizes and
+layouts, raw .bin export (CPU, gloo)."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import dummygrad_b200 as dg
+from dummygrad_b200 import checkpoint
+from dummygrad_b200.models.gpt import GPT
+from dummygrad_b200.parallel.trainer import Trainer
+
+V, S, D, H, L_, FF = 64, 16, 32, 4, 2, 64
+
+
+def _data(step, B):
+    g = torch.Generator().manual_seed(1000 + step)
+    ids = torch.randint(0, V, (B, S), generator=g)
+    return ids, torch.roll(ids, -1, 1).reshape(-1)
+
+
+def _model(seed):
+    dg.manual_seed(seed)
+    return GPT(V, S, D, H, L_, d_ff=FF, dtype=torch.float32, device=torch.device("cpu"))
+
+
+def _run(rank, world, port, tmp, q):
+    if world > 1:
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    B = 4
+    tr = Trainer(_model(1), micro_batch=B // world, lr=1e-2, comm="collective", bucket_mb=0.01)
+    sl = slice(rank * B // world, (rank + 1) * B // world)
+
+    def steps(t, a, b):
+        out = []
+        for s in range(a, b):
+            ids, tg = _data(s, B)
+            out.append(t.step(ids[sl], tg.reshape(B, S)[sl].reshape(-1)))
+        return out
+
+    steps(tr, 0, 3)
+    h = tr.save(os.path.join(tmp, f"ck{world}"), step=3, config={"note": "test"})
+    cont = steps(tr, 3, 6)           # training goes on while the writer thread runs
+    h.wait()
+    w_after = torch.cat([p.data.reshape(-1) for p in tr.model.parameters()]).tolist()
+    tr2 = Trainer(_model(99), micro_batch=B // world, lr=1e-2, comm="collective", bucket_mb=0.01)
+    man = tr2.load(os.path.join(tmp, f"ck{world}"))
+    resumed = steps(tr2, 3, 6)
+    if rank == 0:
+        q.put((world, cont, resumed, man["step"], man["optimizer_t"], w_after))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_resume_is_bitwise_identical(world):
+    with tempfile.TemporaryDirectory() as tmp:
+        ctx = mp.get_context("spawn")
+        import queue
+        q = ctx.SimpleQueue() if world > 1 else queue.SimpleQueue()   # in-process: no pipe to fill up
+        port = 29650 + world
+        if world == 1:
+            _run(0, 1, port, tmp, q)
+        else:
+            procs = [ctx.Process(target=_run, args=(r, world, port, tmp, q)) for r in range(world)]
+            [p.start() for p in procs]
+        w, cont, resumed, step, t, _ = q.get()      # before join: a large item blocks the sender until read
+        if world > 1:
+            [p.join(180) for p in procs]
+            assert all(p.exitcode == 0 for p in procs)
+        assert step == 3 and t == 3
+        assert cont == resumed, (cont, resumed)          # float equality = bitwise for finite values
+
+
+def test_reshard_dp2_to_dp1_and_export(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_run, args=(r, 2, 29655, str(tmp_path), q)) for r in range(2)]
+    [p.start() for p in procs]
+    _, _, _, _, _, w2 = q.get()
+    [p.join(180) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+    # load the 2-rank checkpoint into a 1-rank engine: same weights, same optimizer state
+    tr = Trainer(_model(5), micro_batch=4, lr=1e-2, comm="collective", bucket_mb=0.01)
+    tr.load(str(tmp_path / "ck2"))
+    for s in range(3, 6):
+        ids, tg = _data(s, 4)
+        tr.step(ids, tg)
+    # the 2-rank run averaged two half-batch gradients, this one sees the whole batch: equal up to rounding
+    w1 = torch.cat([p.data.reshape(-1) for p in tr.model.parameters()]).numpy()
+    # (Adam divides by sqrt(v): elements whose gradient is ~0 amplify rounding, so bound mean and max)
+    d = np.abs(w1 - np.array(w2, dtype=np.float32))
+    assert d.mean() < 1e-5 and d.max() < 5e-3, (d.mean(), d.max())
+    # raw fp32 export == what the freshly loaded model holds, in parameters() order
+    tr3 = Trainer(_model(6), micro_batch=4, lr=1e-2, comm="collective", bucket_mb=0.01)
+    tr3.load(str(tmp_path / "ck2"))
+    n = checkpoint.export_bin(str(tmp_path / "ck2"), str(tmp_path / "w.bin"))
+    flat = np.fromfile(tmp_path / "w.bin", dtype="<f4")
+    assert n == flat.size == sum(p.size() for p in tr3.model.parameters())
+    want = np.concatenate([p.data.reshape(-1).numpy() for p in tr3.model.parameters()])
+    np.testing.assert_array_equal(flat, want)
+    m2 = _model(7)
+    checkpoint.load_parameters(str(tmp_path / "w.bin"), m2.parameters())
+    for a, b in zip(m2.parameters(), tr3.model.parameters()):
+        assert torch.equal(a.data, b.data)
+    checkpoint.save_parameters(str(tmp_path / "w2.bin"), m2.parameters())
+    assert open(tmp_path / "w2.bin", "rb").read() == open(tmp_path / "w.bin", "rb").read()
+
+
+def test_reader_rejects_incomplete_coverage(tmp_path):
+    tr = Trainer(_model(1), micro_batch=2, lr=1e-2, comm="collective")
+    tr.save(str(tmp_path / "ck"), step=0, asynchronous=False).wait()
+    import json
+    idx = json.load(open(tmp_path / "ck" / "rank00000.json"))
+    idx["pieces"] = idx["pieces"][3:]
+    json.dump(idx, open(tmp_path / "ck" / "rank00000.json", "w"))
+    with pytest.raises(ValueError, match="cover"):
+        Trainer(_model(2), micro_batch=2, comm="collective").load(str(tmp_path / "ck"))
+
+
+# ----------------------------------------------------------------------------- tensor parallel
+def _tp_run(rank, world, port, tmp, q):
+    import os as _os
+    _os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    dg.set_default_device("cpu")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dummygrad_b200.parallel.trainer import TPTrainer
+    dims = (48, 8, 16, 4, 2, 32)
+    B, S_ = 4, 8
+
+    def batch(step):
+        g = torch.Generator().manual_seed(500 + step)
+        ids = torch.randint(0, 48, (B, S_), generator=g)
+        return ids, torch.roll(ids, -1, 1).reshape(-1)
+
+    def steps(t, a, b):
+        return [float(t.step_device(*batch(s)).item()) for s in range(a, b)]
+
+    dg.manual_seed(3)
+    tr = TPTrainer(dims, tp_size=world, micro_batch=B, seq_len=S_, lr=1e-2, comm="collective", dtype=torch.float32,
+                   device="cpu")
+    steps(tr, 0, 2)
+    h = tr.save(_os.path.join(tmp, "tp"), step=2)
+    cont = steps(tr, 2, 4)
+    h.wait()
+    dg.manual_seed(77)
+    tr2 = TPTrainer(dims, tp_size=world, micro_batch=B, seq_len=S_, lr=1e-2, comm="collective", dtype=torch.float32,
+                    device="cpu")
+    tr2.load(_os.path.join(tmp, "tp"))
+    resumed = steps(tr2, 2, 4)
+    if rank == 0:
+        q.put((cont, resumed))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_checkpoint_resume_and_reshard_to_one_rank(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_tp_run, args=(r, 2, 29661, str(tmp_path), q)) for r in range(2)]
+    [p.start() for p in procs]
+    cont, resumed = q.get()
+    [p.join(180) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+    assert cont == resumed
+    # the 2-way sharded checkpoint reassembles into logical [d, d] / [d, ff] tensors ...
+    rd = checkpoint.CheckpointReader(str(tmp_path / "tp"))
+    names = [p["name"] for p in rd.manifest["params"]]
+    assert rd.shapes[names.index("blocks.0.attn.W_q.W")] == (16, 16)
+    assert rd.shapes[names.index("blocks.0.ffn.fc2.W")] == (32, 16)
+    # ... and loads into an un-sharded model and into the data-parallel engine of the plain GPT
+    from dummygrad_b200.parallel.trainer import TPTrainer
+    dg.set_default_device("cpu")
+    one = TPTrainer((48, 8, 16, 4, 2, 32), tp_size=1, micro_batch=4, seq_len=8, comm="collective", dtype=torch.float32,
+                    device="cpu")
+    one.load(str(tmp_path / "tp"))
+    i = names.index("blocks.1.ffn.fc1.W")
+    assert torch.equal(one.model.parameters()[i].data, rd.full(i, "master"))
+    assert torch.equal(one.opt.state[i].v, rd.full(i, "v"))
+    dg.manual_seed(1)
+    plain = Trainer(GPT(48, 8, 16, 4, 2, d_ff=32, dtype=torch.float32, device=torch.device("cpu")), micro_batch=4,
+                    comm="collective")
+    plain.load(str(tmp_path / "tp"))
+    for a, b in zip(plain.model.parameters(), one.model.parameters()):
+        assert torch.equal(a.data, b.data)
