@@ -63,22 +63,23 @@ class SaveHandle:
         self.error: BaseException | None = None
 
     def wait(self) -> None:
-        """Join the writer, then (rank 0, after every rank is done) publish the manifest."""
+        """Join this rank's writer thread. No collective is involved: a checkpoint counts as complete
+        when the manifest and the index file of every writer it lists exist (``is_complete``), so a
+        rank that dies mid-save cannot block the others or leave a half checkpoint that looks whole."""
         if self._thread is not None:
             self._thread.join()
             self._thread = None
         if self.error is not None:
             raise RuntimeError(f"checkpoint write failed: {self.error}") from self.error
-        if dist.is_initialized():
-            dist.barrier(self._group)
-        if self._manifest is not None:
-            tmp = os.path.join(self.dirpath, "manifest.json.tmp")
-            with open(tmp, "w") as f:
-                json.dump(self._manifest, f, indent=1)
-            os.replace(tmp, os.path.join(self.dirpath, "manifest.json"))
-            self._manifest = None
-        if dist.is_initialized():
-            dist.barrier(self._group)
+
+
+def is_complete(dirpath: str) -> bool:
+    try:
+        with open(os.path.join(dirpath, "manifest.json")) as f:
+            man = json.load(f)
+    except (OSError, ValueError):
+        return False
+    return all(os.path.isfile(os.path.join(dirpath, f"rank{r:05d}.json")) for r in man.get("writers", []))
 
 
 def _write_pieces(dirpath: str, writer_rank: int, pieces: list[tuple[dict, torch.Tensor]], manifest: dict | None,
@@ -125,11 +126,14 @@ def _write_pieces(dirpath: str, writer_rank: int, pieces: list[tuple[dict, torch
             with open(base + ".json.tmp", "w") as f:
                 json.dump({"file": os.path.basename(base) + ".bin", "pieces": index}, f)
             os.replace(base + ".json.tmp", base + ".json")
+            if manifest is not None:
+                tmp = os.path.join(dirpath, "manifest.json.tmp")
+                with open(tmp, "w") as f:
+                    json.dump(manifest, f, indent=1)
+                os.replace(tmp, os.path.join(dirpath, "manifest.json"))
         except BaseException as e:  # surfaced by wait()
             handle.error = e
 
-    if total == 0 and not pieces:
-        return handle
     if asynchronous:
         handle._thread = threading.Thread(target=work, name="dg-checkpoint-writer", daemon=True)
         handle._thread.start()
@@ -154,10 +158,11 @@ def restore_rng(manifest: dict) -> None:
 
 
 def _manifest(params: Sequence, shapes: Sequence[Sequence[int]], names: Sequence[str] | None, step: int, opt_t: int,
-              config, layout: dict, extra: dict | None) -> dict:
+              config, layout: dict, extra: dict | None, writers: Sequence[int] = (0,)) -> dict:
     names = list(names) if names is not None else [f"param{i:04d}" for i in range(len(params))]
     cfg = config.to_dict() if hasattr(config, "to_dict") else (config or {})
     return {"format": FORMAT, "step": int(step), "optimizer_t": int(opt_t), "layout": layout,
+            "writers": [int(r) for r in writers],
             "params": [{"name": n, "shape": [int(s) for s in sh], "dtype": str(p.dtype).replace("torch.", "")}
                        for n, sh, p in zip(names, shapes, params)],
             "rng": _rng_state(), "config": cfg, "extra": extra or {}}
@@ -173,6 +178,8 @@ class CheckpointReader:
             self.manifest = json.load(f)
         if self.manifest.get("format") != FORMAT:
             raise ValueError(f"{dirpath}: not a {FORMAT} checkpoint")
+        if not is_complete(dirpath):
+            raise ValueError(f"{dirpath}: incomplete checkpoint (a writer's files are missing)")
         self.shapes = [tuple(p["shape"]) for p in self.manifest["params"]]
         self._pieces: dict[tuple[int, str], list[tuple[dict, np.memmap]]] = {}
         for fn in sorted(os.listdir(dirpath)):
@@ -248,7 +255,7 @@ def save_dp(dirpath: str, dp, *, step: int, config=None, names=None, extra=None,
     man = None
     if dp.rank == 0:
         man = _manifest(dp.params, [p.data.shape for p in dp.params], names, step, dp.t, config,
-                        {"kind": "dp", "world": dp.world}, extra)
+                        {"kind": "dp", "world": dp.world}, extra, writers=range(dp.world))
     return _write_pieces(dirpath, dp.rank, pieces, man, dp.group, asynchronous)
 
 
@@ -310,8 +317,8 @@ def save_tp(dirpath: str, model, opt, ctx, *, step: int, dp_rank: int = 0, confi
     man = None
     if rank == 0:
         man = _manifest(params, shapes, [n for n, _ in layout], step, opt.t, config,
-                        {"kind": "tp", "tp": ctx.world}, extra)
-    return _write_pieces(dirpath, rank, pieces, man, group, asynchronous) if pieces else SaveHandle(dirpath, None, man, group)
+                        {"kind": "tp", "tp": ctx.world}, extra, writers=range(ctx.world))
+    return _write_pieces(dirpath, rank, pieces, man, group, asynchronous) if pieces else SaveHandle(dirpath, None, None, group)
 
 
 def load_tp(dirpath: str, model, opt, ctx) -> dict:

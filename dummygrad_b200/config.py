@@ -1,0 +1,244 @@
+"""One configuration object for a training run.
+
+The reference has no configuration system at all: hyper-parameters are literals in ``main()``
+(src/test_transformer.cpp:10-18, src/mars.cpp:184-198) and defaults live in constructor signatures
+(src/optimizers.h:29, src/layernorm.h:17, src/transformer.h:16). Here one dataclass tree carries
+model, precision, parallel layout, optimizer, communication switches, timeouts, debugging and
+host-side fault injection; it loads from JSON and from ``--section.key value`` command-line
+overrides and is echoed into every log line and checkpoint manifest.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from typing import Any, Sequence
+
+
+@dataclass
+class ModelConfig:
+    family: str = "gpt"            # gpt | mlp
+    preset: str | None = None      # name in dummygrad_b200.models.gpt.PRESETS; overrides the sizes below
+    vocab_size: int = 256
+    max_seq_len: int = 32
+    d_model: int = 64
+    n_heads: int = 4
+    n_layers: int = 2
+    d_ff: int = 256
+    mlp_sizes: tuple[int, ...] = (784, 128, 10)
+
+
+@dataclass
+class ParallelConfig:
+    dp: int = 1                    # data-parallel replicas
+    tp: int = 1                    # tensor-parallel width (sequence-parallel activations inside)
+    pp: int = 1                    # pipeline stages: no config needs it; only 1 is accepted
+    comm: str = "fused"            # fused = own kernels over peer memory | collective = NCCL/gloo baseline
+    bucket_mb: float = 64.0
+    max_comm_ctas: int = 32
+
+
+@dataclass
+class OptimizerConfig:
+    name: str = "adamw"            # adamw | adam | sgd
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+
+
+@dataclass
+class DataConfig:
+    global_batch: int = 8
+    micro_batch: int = 8
+    seq_len: int = 32
+    seed: int = 0
+
+
+@dataclass
+class RuntimeConfig:
+    dtype: str = "bf16"            # bf16 (fp32 master weights) | fp32
+    steps: int = 10
+    warmup: int = 3
+    wait_seconds: float = 20.0     # limit of every device-side flag wait
+    heartbeat_seconds: float = 5.0
+    heartbeat_timeout: float = 60.0
+    checkpoint_dir: str | None = None
+    checkpoint_every: int = 0
+    metrics_path: str | None = None
+    profile_ops: bool = False
+    debug_bounds: bool = False
+
+
+@dataclass
+class FaultConfig:
+    """Host-side fault injection (never a device fault): at step ``at_step`` the rank ``rank`` does
+    ``kind``: none | exit | raise | sleep | skip_heartbeat | skip_signal."""
+    kind: str = "none"
+    rank: int = 0
+    at_step: int = -1
+    seconds: float = 0.0
+
+
+@dataclass
+class Config:
+    model: ModelConfig = field(default_factory=ModelConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    data: DataConfig = field(default_factory=DataConfig)
+    runtime: RuntimeConfig = field(default_factory=RuntimeConfig)
+    fault: FaultConfig = field(default_factory=FaultConfig)
+
+    # ------------------------------------------------------------------ (de)serialisation
+    def to_dict(self) -> dict:
+        return dataclasses.asdict(self)
+
+    def to_json(self, path: str | None = None) -> str:
+        text = json.dumps(self.to_dict(), indent=1)
+        if path:
+            with open(path, "w") as f:
+                f.write(text)
+        return text
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "Config":
+        cfg = cls()
+        for sec, values in d.items():
+            if not hasattr(cfg, sec):
+                raise KeyError(f"unknown config section '{sec}'")
+            sub = getattr(cfg, sec)
+            for k, v in values.items():
+                _set(sub, sec, k, v)
+        cfg.validate()
+        return cfg
+
+    @classmethod
+    def from_json(cls, path: str) -> "Config":
+        with open(path) as f:
+            return cls.from_dict(json.load(f))
+
+    @classmethod
+    def from_preset(cls, name: str) -> "Config":
+        if name not in PRESETS:
+            raise KeyError(f"unknown preset '{name}' (have: {', '.join(PRESETS)})")
+        return cls.from_dict(PRESETS[name])
+
+    def override(self, args: Sequence[str]) -> "Config":
+        """Apply ``--section.key value`` (or ``--section.key=value``) pairs, in order."""
+        i = 0
+        args = list(args)
+        while i < len(args):
+            a = args[i]
+            if not a.startswith("--") or "." not in a:
+                raise ValueError(f"expected --section.key, got '{a}'")
+            if "=" in a:
+                key, val = a[2:].split("=", 1)
+                i += 1
+            else:
+                if i + 1 >= len(args):
+                    raise ValueError(f"'{a}' needs a value")
+                key, val = a[2:], args[i + 1]
+                i += 2
+            sec, k = key.split(".", 1)
+            if not hasattr(self, sec):
+                raise KeyError(f"unknown config section '{sec}'")
+            _set(getattr(self, sec), sec, k, val)
+        self.validate()
+        return self
+
+    # ------------------------------------------------------------------ checks
+    def validate(self) -> None:
+        p, d = self.parallel, self.data
+        if p.pp != 1:
+            raise ValueError("pipeline parallelism is not implemented (no configuration needs it); parallel.pp must be 1")
+        if p.comm not in ("fused", "collective"):
+            raise ValueError("parallel.comm must be 'fused' or 'collective'")
+        if self.runtime.dtype not in ("bf16", "fp32"):
+            raise ValueError("runtime.dtype must be 'bf16' or 'fp32'")
+        if self.optimizer.name not in ("adamw", "adam", "sgd"):
+            raise ValueError("optimizer.name must be adamw, adam or sgd")
+        if d.global_batch % p.dp:
+            raise ValueError("data.global_batch must be a multiple of parallel.dp")
+        if (d.global_batch // p.dp) % min(d.micro_batch, d.global_batch // p.dp):
+            raise ValueError("the per-replica batch must be a multiple of data.micro_batch")
+        if self.fault.kind not in ("none", "exit", "raise", "sleep", "skip_heartbeat", "skip_signal"):
+            raise ValueError(f"unknown fault kind '{self.fault.kind}'")
+        m = self.resolved_model()
+        if m.family == "gpt":
+            if m.d_model % m.n_heads:
+                raise ValueError("model.d_model must be divisible by model.n_heads")
+            if m.n_heads % p.tp or m.d_ff % p.tp:
+                raise ValueError("model.n_heads and model.d_ff must be divisible by parallel.tp")
+            if d.seq_len > m.max_seq_len:
+                raise ValueError("data.seq_len exceeds model.max_seq_len")
+
+    def resolved_model(self) -> ModelConfig:
+        """The model section with a named preset expanded into sizes."""
+        m = self.model
+        if m.preset:
+            from .models.gpt import PRESETS as GPT_PRESETS
+            v, s, dm, h, l, ff = GPT_PRESETS[m.preset]
+            return dataclasses.replace(m, vocab_size=v, max_seq_len=s, d_model=dm, n_heads=h, n_layers=l, d_ff=ff)
+        return m
+
+    @property
+    def world_size(self) -> int:
+        return self.parallel.dp * self.parallel.tp
+
+
+def _set(obj: Any, sec: str, key: str, value: Any) -> None:
+    fields = {f.name: f for f in dataclasses.fields(obj)}
+    if key not in fields:
+        raise KeyError(f"unknown config key '{sec}.{key}'")
+    cur = getattr(obj, key)
+    if isinstance(value, str):       # from the command line: coerce to the field's type
+        t = fields[key].type
+        if isinstance(cur, bool) or t == "bool":
+            value = value.lower() in ("1", "true", "yes", "on")
+        elif isinstance(cur, int) or t == "int":
+            value = int(value)
+        elif isinstance(cur, float) or t == "float":
+            value = float(value)
+        elif isinstance(cur, tuple):
+            value = tuple(int(x) for x in value.split(",") if x)
+        elif value.lower() in ("none", "null") and "None" in str(t):
+            value = None
+    elif isinstance(cur, tuple) and isinstance(value, list):
+        value = tuple(value)
+    setattr(obj, key, value)
+
+
+# The five benchmark configurations as committed presets.
+PRESETS: dict[str, dict] = {
+    "mlp": {
+        "model": {"family": "mlp", "mlp_sizes": [784, 128, 10]},
+        "optimizer": {"name": "sgd", "lr": 1e-2},
+        "data": {"global_batch": 64, "micro_batch": 64, "seq_len": 1, "seed": 0},
+        "runtime": {"dtype": "fp32", "steps": 100},
+    },
+    "toy": {
+        "model": {"preset": "toy"},
+        "optimizer": {"name": "adam", "lr": 3e-4, "beta2": 0.999},
+        "data": {"global_batch": 8, "micro_batch": 8, "seq_len": 32},
+        "runtime": {"dtype": "fp32"},
+    },
+    "gpt350m_dp8": {
+        "model": {"preset": "gpt350m"},
+        "parallel": {"dp": 8, "tp": 1, "comm": "fused"},
+        "optimizer": {"name": "adamw", "lr": 3e-4, "weight_decay": 0.1},
+        "data": {"global_batch": 64, "micro_batch": 8, "seq_len": 1024},
+    },
+    "gpt1p3b_tp8": {
+        "model": {"preset": "gpt1p3b"},
+        "parallel": {"dp": 1, "tp": 8, "comm": "fused"},
+        "optimizer": {"name": "adamw", "lr": 2e-4, "weight_decay": 0.1},
+        "data": {"global_batch": 32, "micro_batch": 8, "seq_len": 2048},
+    },
+    "gpt1p3b_tp2dp4": {
+        "model": {"preset": "gpt1p3b"},
+        "parallel": {"dp": 4, "tp": 2, "comm": "fused"},
+        "optimizer": {"name": "adamw", "lr": 2e-4, "weight_decay": 0.1},
+        "data": {"global_batch": 32, "micro_batch": 8, "seq_len": 2048},
+    },
+}

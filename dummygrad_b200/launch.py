@@ -1,0 +1,76 @@
+"""Single-node launcher with restart: ``python -m dummygrad_b200.launch --nproc N [--max-restarts R]
+[--shrink] -- <args of dummygrad_b200.run>``.
+
+Starts one ``dummygrad_b200.run`` process per rank, waits, and when the job ends with a failure
+(a rank died or reported a peer failure) stops the remaining ranks BY PID, then starts the job
+again; the run resumes from its newest complete checkpoint. With ``--shrink`` the restart uses one
+rank fewer per restart that followed a rank's death ("elastic" in the restart sense: checkpoints
+re-shard to any data-parallel size).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import socket
+import subprocess
+import sys
+import time
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def run_once(nproc: int, run_args: list[str], env_extra: dict | None = None, poll: float = 0.2) -> list[int]:
+    """Start nproc ranks, return their exit codes. When one rank fails the others get a grace
+    period to notice through the watchdog, then are terminated by PID."""
+    port = _free_port()
+    procs = []
+    for r in range(nproc):
+        env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(nproc), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), **(env_extra or {}))
+        procs.append(subprocess.Popen([sys.executable, "-m", "dummygrad_b200.run", *run_args], env=env))
+    grace = float(os.environ.get("DG_LAUNCH_GRACE", "30"))
+    first_fail = None
+    while any(p.poll() is None for p in procs):
+        time.sleep(poll)
+        if first_fail is None and any(p.poll() not in (None, 0) for p in procs):
+            first_fail = time.time()
+        if first_fail is not None and time.time() - first_fail > grace:
+            for p in procs:
+                if p.poll() is None:
+                    p.terminate()
+            time.sleep(1.0)
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+    return [p.wait() for p in procs]
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--nproc", type=int, default=1)
+    ap.add_argument("--max-restarts", type=int, default=2)
+    ap.add_argument("--shrink", action="store_true", help="restart with one rank fewer after a rank died")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    a = ap.parse_args(argv)
+    run_args = a.rest[1:] if a.rest and a.rest[0] == "--" else a.rest
+    nproc = a.nproc
+    for attempt in range(a.max_restarts + 1):
+        codes = run_once(nproc, run_args)
+        if all(c == 0 for c in codes):
+            return 0
+        print(f"[launch] attempt {attempt}: exit codes {codes}", file=sys.stderr, flush=True)
+        # fault injection is for the first attempt only: a restarted job must not re-inject
+        run_args = [x for x in run_args] + ["--fault.kind", "none"]
+        if a.shrink and nproc > 1:
+            nproc -= 1
+    return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,187 @@
+"""Failure detection for multi-process training: heartbeats, a watchdog thread and host-side
+fault injection.
+
+The reference has no failure handling beyond ``throw std::runtime_error`` on misuse (and
+src/mars.cpp:254-260 swallows exceptions and prints success - not reproduced here).
+
+Design:
+* Device side, every wait on a peer flag is bounded; when it expires the kernel records a status
+  code, leaves through its normal exit and the host raises (``Trainer.check``).
+* Host side, every rank publishes a heartbeat counter in a key-value store (a ``TCPStore`` side
+  channel, independent of NCCL) from a daemon thread. A second thread watches the peers: a
+  heartbeat older than ``timeout`` seconds, an explicit ``fail/<rank>`` key, or a non-zero status
+  callback marks the job failed. The training loop calls ``check()`` between steps - never with
+  kernels or collectives in flight - and gets a ``PeerFailure``; the launcher then restarts the
+  job from the last checkpoint, possibly at a smaller world size (checkpoints re-shard).
+* Fault injection is host-side only: a chosen rank exits, raises, sleeps or stops its heartbeat at
+  a chosen step. On GPUs the only injected failure is a skipped signal, which the bounded wait
+  converts into an error status.
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from typing import Callable
+
+import torch.distributed as dist
+
+
+class PeerFailure(RuntimeError):
+    """Another rank stopped responding or reported a failure."""
+
+
+class InjectedFault(RuntimeError):
+    """Raised by FaultInjector(kind='raise')."""
+
+
+class Watchdog:
+    def __init__(self, store, rank: int, world: int, *, interval: float = 1.0, timeout: float = 10.0,
+                 status_fn: Callable[[], int] | None = None, on_failure: Callable[[str], None] | None = None,
+                 prefix: str = "dg"):
+        self.store, self.rank, self.world = store, rank, world
+        self.interval, self.timeout = interval, timeout
+        self.status_fn, self.on_failure = status_fn, on_failure
+        self.prefix = prefix
+        self._stop = threading.Event()
+        self._beat_enabled = threading.Event()
+        self._beat_enabled.set()
+        self.failure: str | None = None
+        self._threads: list[threading.Thread] = []
+        self._count = 0
+
+    # ------------------------------------------------------------------ keys
+    def _hb(self, r: int) -> str:
+        return f"{self.prefix}/hb/{r}"
+
+    def _fail(self, r: int) -> str:
+        return f"{self.prefix}/fail/{r}"
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self) -> "Watchdog":
+        self._beat_once()
+        for fn, name in ((self._beat_loop, "dg-heartbeat"), (self._watch_loop, "dg-watchdog")):
+            t = threading.Thread(target=fn, name=name, daemon=True)
+            t.start()
+            self._threads.append(t)
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        for t in self._threads:
+            t.join(timeout=2 * self.interval + 1)
+        self._threads.clear()
+
+    def pause_heartbeat(self) -> None:
+        """Fault injection: this rank goes silent (peers will declare it dead)."""
+        self._beat_enabled.clear()
+
+    def report_failure(self, reason: str) -> None:
+        """Tell the peers that this rank is going down (e.g. from an exception handler)."""
+        try:
+            self.store.set(self._fail(self.rank), reason)
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ threads
+    def _beat_once(self) -> None:
+        self._count += 1
+        self.store.set(self._hb(self.rank), f"{self._count}:{time.time():.3f}")
+
+    def _beat_loop(self) -> None:
+        while not self._stop.wait(self.interval):
+            if self._beat_enabled.is_set():
+                try:
+                    self._beat_once()
+                except Exception as e:      # the store itself is gone: rank 0 (its host) died
+                    self._declare(f"heartbeat store unreachable: {e}")
+                    return
+
+    def _watch_loop(self) -> None:
+        last_seen: dict[int, tuple[str, float]] = {}
+        started = time.time()
+        while not self._stop.wait(self.interval):
+            now = time.time()
+            try:
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    if self.store.check([self._fail(r)]):
+                        self._declare(f"rank {r} reported: {self.store.get(self._fail(r)).decode()}")
+                        return
+                    if self.store.check([self._hb(r)]):
+                        val = self.store.get(self._hb(r)).decode()
+                        if r not in last_seen or last_seen[r][0] != val:
+                            last_seen[r] = (val, now)
+                    seen_at = last_seen[r][1] if r in last_seen else started
+                    if now - seen_at > self.timeout:
+                        self._declare(f"rank {r}: no heartbeat for {now - seen_at:.1f} s")
+                        return
+            except Exception as e:
+                self._declare(f"heartbeat store unreachable: {e}")
+                return
+            if self.status_fn is not None:
+                code = self.status_fn()
+                if code:
+                    self._declare(f"device status word 0x{code:x} (a bounded wait expired)")
+                    return
+
+    def _declare(self, reason: str) -> None:
+        if self.failure is None:
+            self.failure = reason
+            if self.on_failure is not None:
+                self.on_failure(reason)
+
+    # ------------------------------------------------------------------ main-thread API
+    def check(self) -> None:
+        """Call between steps, with no kernel or collective in flight."""
+        if self.failure is not None:
+            raise PeerFailure(self.failure)
+
+
+def abort_process_group() -> None:
+    """Tear the default process group down without waiting for peers (best effort)."""
+    if not dist.is_initialized():
+        return
+    try:
+        from torch.distributed.distributed_c10d import _abort_process_group  # type: ignore
+        _abort_process_group()
+    except Exception:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+class FaultInjector:
+    """Host-side fault injection driven by the ``fault`` section of the config."""
+
+    EXIT_CODE = 17
+
+    def __init__(self, kind: str = "none", rank: int = 0, at_step: int = -1, seconds: float = 0.0,
+                 watchdog: Watchdog | None = None):
+        self.kind, self.rank, self.at_step, self.seconds, self.watchdog = kind, rank, at_step, seconds, watchdog
+        self.skip_signal = False    # read by code that signals a peer flag (tests of the bounded wait)
+
+    @classmethod
+    def from_config(cls, fc, watchdog: Watchdog | None = None) -> "FaultInjector":
+        return cls(fc.kind, fc.rank, fc.at_step, fc.seconds, watchdog)
+
+    def at(self, step: int, my_rank: int) -> None:
+        """Call at the top of every step (between steps: nothing of this rank is in flight)."""
+        if self.kind == "none" or my_rank != self.rank or step != self.at_step:
+            return
+        if self.kind == "exit":
+            os._exit(self.EXIT_CODE)
+        if self.kind == "raise":
+            if self.watchdog is not None:
+                self.watchdog.report_failure("injected exception")
+            raise InjectedFault(f"injected at step {step}")
+        if self.kind == "sleep":
+            time.sleep(self.seconds)
+        elif self.kind == "skip_heartbeat":
+            if self.watchdog is not None:
+                self.watchdog.pause_heartbeat()
+            time.sleep(self.seconds)
+        elif self.kind == "skip_signal":
+            self.skip_signal = True

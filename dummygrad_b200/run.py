@@ -1,0 +1,194 @@
+"""Config-driven training entry point: ``python -m dummygrad_b200.run --preset toy [--section.key value ...]``.
+
+One process per GPU (started by ``torch.distributed.run`` or by ``dummygrad_b200.launch``); on a
+machine without GPUs the same loop runs on CPU ranks over gloo with the collective baseline path.
+The loop ties the subsystems together: synthetic data from pinned host memory, the data-parallel
+or tensor-parallel trainer, per-step metrics, periodic asynchronous checkpoints, resume from the
+newest complete checkpoint, heartbeat watchdog and host-side fault injection.
+
+Exit codes: 0 finished; 75 a peer failed (restart from the last checkpoint); 17 injected exit.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+from .config import Config
+
+EXIT_PEER_FAILURE = 75
+
+
+def latest_checkpoint(root: str | None) -> str | None:
+    """Newest ``step_NNNNNNNN`` directory under root that is complete (manifest + every writer's files)."""
+    if not root or not os.path.isdir(root):
+        return None
+    from .checkpoint import is_complete
+    done = sorted(d for d in os.listdir(root) if d.startswith("step_") and is_complete(os.path.join(root, d)))
+    return os.path.join(root, done[-1]) if done else None
+
+
+def synthetic_batch(cfg: Config, step: int, replica: int, pin: bool):
+    """Uniform random tokens for one data-parallel replica; a function of (seed, step, replica) only,
+    so a resumed or re-sharded run sees the same global batch."""
+    m, d = cfg.resolved_model(), cfg.data
+    per = d.global_batch // cfg.parallel.dp
+    g = torch.Generator().manual_seed(d.seed * 1_000_003 + step)
+    ids = torch.randint(0, m.vocab_size, (d.global_batch, d.seq_len), generator=g)
+    ids = ids[replica * per:(replica + 1) * per].contiguous()
+    tgt = torch.roll(ids, -1, 1).reshape(-1).contiguous()
+    return (ids.pin_memory(), tgt.pin_memory()) if pin else (ids, tgt)
+
+
+def main(argv: list[str] | None = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    cfg = Config()
+    if argv and argv[0] == "--preset":
+        cfg = Config.from_preset(argv[1])
+        argv = argv[2:]
+    elif argv and argv[0] == "--config":
+        cfg = Config.from_json(argv[1])
+        argv = argv[2:]
+    cfg.override(argv)
+
+    import dummygrad_b200 as dg
+    from .parallel.watchdog import FaultInjector, InjectedFault, PeerFailure, Watchdog, abort_process_group
+    from .utils.metrics import MetricsLogger, StepTimer, gpt_flops_per_token
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(local)
+    device = torch.device("cuda", local) if cuda else torch.device("cpu")
+    dg.set_default_device(device)
+    if world != cfg.world_size:
+        # elastic restart at another size: keep tp, let dp absorb the change
+        if world % cfg.parallel.tp:
+            raise SystemExit(f"world size {world} is not a multiple of parallel.tp={cfg.parallel.tp}")
+        cfg.parallel.dp = world // cfg.parallel.tp
+        cfg.validate()
+    wd = None
+    timers: list = []
+    if world > 1:
+        dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=max(cfg.runtime.heartbeat_timeout, 30.0)),
+                                **({"device_id": device} if cuda else {}))
+        store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), int(os.environ.get("MASTER_PORT", "29500")) + 1,
+                              world, rank == 0, timeout=datetime.timedelta(seconds=60))
+
+        def hard_stop(reason: str) -> None:
+            # The main thread may be blocked inside a collective whose peer is gone. Give it a grace
+            # period to reach check() between steps, then leave from here.
+            def leave():
+                print(f"[rank {rank}] watchdog: {reason}; main thread did not return, exiting", file=sys.stderr, flush=True)
+                abort_process_group()
+                os._exit(EXIT_PEER_FAILURE)
+            t = threading.Timer(max(2 * cfg.runtime.heartbeat_seconds, 2.0), leave)
+            t.daemon = True
+            t.start()
+            timers.append(t)
+
+        wd = Watchdog(store, rank, world, interval=cfg.runtime.heartbeat_seconds, timeout=cfg.runtime.heartbeat_timeout,
+                      on_failure=hard_stop)
+    inject = FaultInjector.from_config(cfg.fault, wd)
+
+    m, rt, par = cfg.resolved_model(), cfg.runtime, cfg.parallel
+    dtype = torch.bfloat16 if rt.dtype == "bf16" else torch.float32
+    dg.manual_seed(cfg.data.seed)
+    if m.family != "gpt":
+        raise SystemExit("run.py trains the GPT family; the MLP benchmark lives in bench.py --config mlp")
+    if par.tp > 1:
+        from .parallel.trainer import TPTrainer
+        trainer = TPTrainer((m.vocab_size, m.max_seq_len, m.d_model, m.n_heads, m.n_layers, m.d_ff), tp_size=par.tp,
+                            micro_batch=cfg.data.micro_batch, seq_len=cfg.data.seq_len, lr=cfg.optimizer.lr,
+                            weight_decay=cfg.optimizer.weight_decay, comm=par.comm, dtype=dtype, device=device)
+        replica = rank // par.tp
+        status_fn = trainer.ctx.check_status
+    else:
+        from .models.gpt import GPT
+        from .parallel.trainer import Trainer
+        model = GPT(m.vocab_size, m.max_seq_len, m.d_model, m.n_heads, m.n_layers, d_ff=m.d_ff, dtype=dtype, device=device)
+        o = cfg.optimizer
+        trainer = Trainer(model, micro_batch=cfg.data.micro_batch, lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
+                          weight_decay=o.weight_decay, optimizer=o.name, comm=par.comm, bucket_mb=par.bucket_mb,
+                          max_comm_ctas=par.max_comm_ctas, wait_seconds=rt.wait_seconds)
+        replica = rank
+        status_fn = trainer.dp.check_status
+
+    start = 0
+    ck = latest_checkpoint(rt.checkpoint_dir)
+    if ck:
+        man = trainer.load(ck)
+        start = int(man["step"])
+    tokens = cfg.data.global_batch * cfg.data.seq_len
+    log = MetricsLogger(rt.metrics_path, tokens_per_step=tokens, config=cfg,
+                        flops_per_token=gpt_flops_per_token(m.d_model, m.n_layers, m.d_ff, m.vocab_size, cfg.data.seq_len))
+    if ck:
+        log.log_event("resume", checkpoint=ck, step=start, world=world)
+    timer = StepTimer(device)
+    if wd:
+        wd.start()
+    pending = None
+    try:
+        for step in range(start, rt.steps):
+            inject.at(step, rank)
+            if wd:
+                wd.check()
+            ids, tgt = synthetic_batch(cfg, step, replica, pin=cuda)
+            timer.start()
+            if par.tp > 1:
+                loss_t = trainer.step_device(ids.to(device, non_blocking=True), tgt.to(device, non_blocking=True))
+                if dist.is_initialized():
+                    dist.all_reduce(loss_t, group=trainer.tp_group)   # ranks of a group hold shares of the mean
+                loss = float(loss_t.item())
+            else:
+                loss = trainer.step(ids, tgt)
+            ms = timer.stop_ms()
+            code = status_fn() if cuda else 0
+            if code:
+                raise PeerFailure(f"device status word 0x{code:x}: a bounded wait expired")
+            log.log_step(step, loss, ms, n_gpus=world)
+            if rt.checkpoint_dir and rt.checkpoint_every and (step + 1) % rt.checkpoint_every == 0:
+                if pending is not None:
+                    pending.wait()
+                pending = trainer.save(os.path.join(rt.checkpoint_dir, f"step_{step + 1:08d}"), step=step + 1, config=cfg)
+        if pending is not None:
+            pending.wait()
+    except Exception as e:
+        # An error inside a collective is usually the first sign of a dead peer: let the watchdog
+        # confirm before deciding between "peer failed" (restartable) and "my own error".
+        peer = isinstance(e, PeerFailure)
+        if wd and not peer and not isinstance(e, InjectedFault):
+            deadline = time.time() + cfg.runtime.heartbeat_timeout + 2 * cfg.runtime.heartbeat_seconds
+            while wd.failure is None and time.time() < deadline:
+                time.sleep(0.05)
+            peer = wd.failure is not None
+        if not peer:
+            if wd:
+                wd.report_failure(f"{type(e).__name__}: {e}")
+            raise
+        for t in timers:
+            t.cancel()
+        reason = wd.failure if (wd and wd.failure) else str(e)
+        log.log_event("peer_failure", reason=reason, rank=rank)
+        print(f"[rank {rank}] stopping: {reason}", file=sys.stderr, flush=True)
+        abort_process_group()
+        os._exit(EXIT_PEER_FAILURE)     # skip destructors that would wait for the dead peer
+    if wd:
+        wd.stop()
+    log.close()
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,114 @@
+"""Per-step metrics as JSON lines.
+
+The reference prints the loss with ``std::cout`` every few steps and nothing else
+(src/test_transformer.cpp:63-65, src/mars.cpp:236). ``MetricsLogger`` writes one JSON object per
+optimizer step (rank 0): loss, device-timed step milliseconds (max over ranks), tokens/s, achieved
+model TFLOP/s and its fraction of the measured bf16 GEMM peak, memory high-water mark, kernel
+launch count and the timeout/status counters of the fused kernels.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def gpt_flops_per_token(d_model: int, n_layers: int, d_ff: int, vocab: int, seq_len: int, causal: bool = True) -> float:
+    """Forward + backward FLOPs per trained token of a decoder (multiply-add = 2 FLOPs, backward =
+    2x forward): linear layers 6 * params_in_matmuls, attention scores and values 12 * L * S * d
+    (halved by the causal mask, which the fused kernel skips)."""
+    per_layer = 4 * d_model * d_model + 2 * d_model * d_ff      # q,k,v,o + two FFN matrices
+    dense = 6.0 * (n_layers * per_layer + vocab * d_model)      # + tied head
+    attn = 12.0 * n_layers * seq_len * d_model * (0.5 if causal else 1.0)
+    return dense + attn
+
+
+def measured_peaks(path: str | None = None) -> dict:
+    """Peak figures measured on this machine (a JSON file with hbm_gbs / bf16_tflops /
+    bf16_tflops_sustained); empty when the file does not exist."""
+    for cand in ([path] if path else []) + [os.environ.get("DG_MEASURED_PEAKS", ""), "MEASURED_PEAKS.json",
+                                            os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")]:
+        if cand and os.path.isfile(cand):
+            with open(cand) as f:
+                return json.load(f)
+    return {}
+
+
+class StepTimer:
+    """CUDA-event (or host clock on CPU) timer whose result is reduced as the max over ranks."""
+
+    def __init__(self, device: torch.device, group=None):
+        self.cuda = device.type == "cuda"
+        self.device, self.group = device, group
+        if self.cuda:
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def start(self) -> None:
+        if self.cuda:
+            self.e0.record()
+        else:
+            self.t0 = time.perf_counter()
+
+    def stop_ms(self) -> float:
+        if self.cuda:
+            self.e1.record()
+            self.e1.synchronize()
+            ms = self.e0.elapsed_time(self.e1)
+        else:
+            ms = (time.perf_counter() - self.t0) * 1e3
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=self.device if self.cuda else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            ms = float(t.item())
+        return ms
+
+
+class MetricsLogger:
+    def __init__(self, path: str | None, *, tokens_per_step: int, flops_per_token: float = 0.0, config=None,
+                 peaks: dict | None = None, rank: int | None = None):
+        self.rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
+        self.tokens_per_step, self.flops_per_token = tokens_per_step, flops_per_token
+        self.peaks = peaks if peaks is not None else measured_peaks()
+        self.records: list[dict] = []
+        self._f = None
+        if path and self.rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+            self._f = open(path, "a")
+            if config is not None:
+                cfg = config.to_dict() if hasattr(config, "to_dict") else config
+                self._write({"event": "config", "config": cfg, "peaks": self.peaks, "time": time.time()})
+
+    def _write(self, rec: dict) -> None:
+        if self._f:
+            self._f.write(json.dumps(rec) + "\n")
+            self._f.flush()
+
+    def log_step(self, step: int, loss: float, step_ms: float, *, n_gpus: int = 1, extra: dict | None = None) -> dict:
+        rec = {"event": "step", "step": step, "loss": loss, "step_ms": step_ms,
+               "tokens_per_s": self.tokens_per_step / (step_ms * 1e-3) if step_ms > 0 else 0.0}
+        if self.flops_per_token:
+            tf = self.flops_per_token * self.tokens_per_step / (step_ms * 1e-3) / 1e12 / max(n_gpus, 1)
+            rec["model_tflops_per_gpu"] = tf
+            peak = self.peaks.get("bf16_tflops_sustained") or self.peaks.get("bf16_tflops")
+            if peak:
+                rec["mfu_of_measured_peak"] = tf / float(peak)
+        if torch.cuda.is_available():
+            rec["hbm_peak_gb"] = torch.cuda.max_memory_allocated() / 2 ** 30
+        if extra:
+            rec.update(extra)
+        if self.rank == 0:
+            self.records.append(rec)
+            self._write(rec)
+        return rec
+
+    def log_event(self, name: str, **fields) -> None:
+        if self.rank == 0:
+            self._write({"event": name, "time": time.time(), **fields})
+
+    def close(self) -> None:
+        if self._f:
+            self._f.close()
+            self._f = None

@@ -1,0 +1,124 @@
+"""Failure detection, fault injection and elastic restart - all on the host (CPU ranks over gloo):
+no GPU is faulted, trapped or hung by any of these tests."""
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch.distributed as dist
+
+from dummygrad_b200.config import Config
+from dummygrad_b200.parallel.watchdog import FaultInjector, InjectedFault, PeerFailure, Watchdog
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_config_roundtrip_and_overrides(tmp_path):
+    c = Config.from_preset("gpt1p3b_tp2dp4")
+    assert c.world_size == 8 and c.resolved_model().d_model == 2048
+    c.override(["--optimizer.lr", "1e-3", "--parallel.comm=collective", "--runtime.checkpoint_dir", "/tmp/x",
+                "--runtime.profile_ops", "true"])
+    assert c.optimizer.lr == 1e-3 and c.parallel.comm == "collective" and c.runtime.profile_ops is True
+    c.to_json(str(tmp_path / "c.json"))
+    assert Config.from_json(str(tmp_path / "c.json")).to_dict() == c.to_dict()
+    with pytest.raises(KeyError):
+        Config().override(["--optimizer.learning_rate", "1"])
+    with pytest.raises(ValueError):
+        Config().override(["--parallel.pp", "2"])
+    with pytest.raises(ValueError):
+        Config.from_preset("gpt350m_dp8").override(["--parallel.tp", "3"])
+    for name in ("mlp", "toy", "gpt350m_dp8", "gpt1p3b_tp8", "gpt1p3b_tp2dp4"):
+        Config.from_preset(name)
+
+
+def _store(port, world, rank):
+    import datetime
+    return dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=datetime.timedelta(seconds=20),
+                         wait_for_workers=False)
+
+
+def test_watchdog_detects_silent_and_reporting_peers():
+    port = 29700 + os.getpid() % 200
+    s0, s1, s2 = _store(port, 3, 0), _store(port, 3, 1), _store(port, 3, 2)
+    seen = []
+    w0 = Watchdog(s0, 0, 3, interval=0.1, timeout=0.8, on_failure=seen.append).start()
+    w1 = Watchdog(s1, 1, 3, interval=0.1, timeout=0.8).start()
+    w2 = Watchdog(s2, 2, 3, interval=0.1, timeout=0.8).start()
+    time.sleep(0.6)
+    w0.check(); w1.check(); w2.check()          # everybody alive
+    w1.pause_heartbeat()                        # rank 1 goes silent
+    t0 = time.time()
+    while w0.failure is None and time.time() - t0 < 5:
+        time.sleep(0.05)
+    assert w0.failure and "rank 1" in w0.failure and seen == [w0.failure]
+    with pytest.raises(PeerFailure):
+        w0.check()
+    assert w2.failure and "rank 1" in w2.failure
+    for w in (w0, w1, w2):
+        w.stop()
+    # an explicit report is seen at once, and a device status word is surfaced
+    s0b, s1b = _store(port + 1, 2, 0), _store(port + 1, 2, 1)
+    status = {"code": 0}
+    a = Watchdog(s0b, 0, 2, interval=0.05, timeout=30, status_fn=lambda: status["code"]).start()
+    b = Watchdog(s1b, 1, 2, interval=0.05, timeout=30).start()
+    b.report_failure("boom")
+    t0 = time.time()
+    while a.failure is None and time.time() - t0 < 3:
+        time.sleep(0.02)
+    assert a.failure and "boom" in a.failure
+    status["code"] = 0x4
+    t0 = time.time()
+    while b.failure is None and time.time() - t0 < 1:
+        time.sleep(0.02)
+    assert b.failure is None                      # b has no status_fn; a's own word is a's problem
+    a.stop(); b.stop()
+    c = Watchdog(_store(port + 2, 1, 0), 0, 1, interval=0.05, timeout=30, status_fn=lambda: 0x4).start()
+    t0 = time.time()
+    while c.failure is None and time.time() - t0 < 3:
+        time.sleep(0.02)
+    assert c.failure and "0x4" in c.failure
+    c.stop()
+
+
+def test_fault_injector_kinds():
+    FaultInjector("none").at(0, 0)
+    with pytest.raises(InjectedFault):
+        FaultInjector("raise", rank=1, at_step=3).at(3, 1)
+    FaultInjector("raise", rank=1, at_step=3).at(3, 0)       # other rank: nothing
+    FaultInjector("raise", rank=1, at_step=3).at(2, 1)       # other step: nothing
+    t0 = time.time()
+    FaultInjector("sleep", at_step=0, seconds=0.2).at(0, 0)
+    assert time.time() - t0 >= 0.2
+    f = FaultInjector("skip_signal", at_step=1)
+    f.at(1, 0)
+    assert f.skip_signal
+
+
+def _launch(tmp_path, nproc, extra, timeout=300):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), DG_LAUNCH_GRACE="20",
+               CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "dummygrad_b200.launch", "--nproc", str(nproc), "--max-restarts", "2", "--shrink", "--",
+           "--preset", "toy", "--runtime.steps", "8", "--runtime.checkpoint_dir", str(tmp_path / "ck"),
+           "--runtime.checkpoint_every", "2", "--runtime.metrics_path", str(tmp_path / "metrics.jsonl"),
+           "--runtime.heartbeat_seconds", "0.2", "--runtime.heartbeat_timeout", "3", "--parallel.comm", "collective",
+           "--parallel.dp", str(nproc), *extra]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout, cwd=ROOT)
+
+
+@pytest.mark.parametrize("kind", ["exit", "raise", "skip_heartbeat"])
+def test_rank_failure_then_restart_smaller_and_resume(tmp_path, kind):
+    extra = ["--fault.kind", kind, "--fault.rank", "1", "--fault.at_step", "5", "--fault.seconds", "30"]
+    r = _launch(tmp_path, 2, extra)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    recs = [json.loads(l) for l in open(tmp_path / "metrics.jsonl")]
+    events = [x["event"] for x in recs]
+    assert "resume" in events, events
+    resume = next(x for x in recs if x["event"] == "resume")
+    assert resume["step"] == 4 and resume["world"] == 1           # newest complete checkpoint, one rank fewer
+    steps = [x["step"] for x in recs if x["event"] == "step"]
+    assert steps[-1] == 7 and set(range(8)) <= set(steps)
+    losses = {x["step"]: x["loss"] for x in recs if x["event"] == "step"}
+    assert all(v == v for v in losses.values())
+    assert "attempt 0" in r.stderr
