@@ -25,7 +25,17 @@ from dummygrad_b200.parallel import dist as D  # noqa: E402
 from dummygrad_b200.parallel import tp  # noqa: E402
 from dummygrad_b200.parallel.dp import DataParallel  # noqa: E402
 
-LINK_GBS = 770.0
+LINK_GBS = 770.0      # measured peer copy, per direction per GPU
+
+
+def _hbm_gbs():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p)).get("hbm_gbs", 6650.0))
+    return 6650.0
+
+
+HBM_GBS = _hbm_gbs()  # measured STREAM-style copy
 
 
 def peak():
@@ -93,9 +103,17 @@ def bench_rs_adam(rank, world, device, emit):
 
         ms_n = timeit(nccl, device)
         link_bytes = 2 * (world - 1) / world * n * 2          # pull grads + push params, per GPU per direction each
-        roof_ms = max((world - 1) / world * n * 2 / (LINK_GBS * 1e9), n / world * 18 / 6.5e12) * 1e3
+        # HBM bytes per GPU: fp32 master + two moments read and written (24 B), own gradient read and own
+        # parameter written (4 B) per owned element; plus the slices of this GPU's gradients that the
+        # peers read and of its parameter buffer that they write (4 B per non-owned element)
+        hbm_bytes = n / world * 28 + (world - 1) / world * n * 4
+        link_ms = (world - 1) / world * n * 2 / (LINK_GBS * 1e9) * 1e3
+        hbm_ms = hbm_bytes / (HBM_GBS * 1e9) * 1e3
+        roof_ms = max(link_ms, hbm_ms)
         emit({"bench": "rs_adam", "world": world, "bucket_mb": mb, "fused_ms": ms, "nccl_ms": ms_n,
-              "nvlink_bytes_per_gpu": link_bytes, "roofline_ms": roof_ms, "frac_of_roofline": roof_ms / ms})
+              "nvlink_bytes_per_gpu": link_bytes, "hbm_bytes_per_gpu": hbm_bytes, "nvlink_ms": link_ms, "hbm_ms": hbm_ms,
+              "roofline_ms": roof_ms, "bound": "hbm" if hbm_ms > link_ms else "nvlink",
+              "frac_of_roofline": roof_ms / ms})
         del dp
 
 

@@ -1,0 +1,214 @@
+"""PyTorch NCCL + cuBLAS baseline for the multi-GPU configurations: the identical decoder written
+with torch.nn (library GEMMs, library flash attention, fused AdamW) and trained with
+DistributedDataParallel, or - for the tensor-parallel configuration - with a hand-rolled
+Megatron-style sequence-parallel layout on NCCL all-gather / reduce-scatter.
+
+This is the yard-stick the framework's own numbers are compared with; nothing here is used by the
+framework. Prints one JSON line in the format of bench.py.
+
+  python -m torch.distributed.run --nproc-per-node N bench/torch_baseline.py --config gpt350m
+  python -m torch.distributed.run --nproc-per-node 8 bench/torch_baseline.py --config gpt1p3b --parallel tp8
+"""
+import argparse
+import json
+import math
+import os
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+CONFIGS = {  # vocab, seq, d, heads, layers, ff, global batch, default micro batch
+    "gpt350m": (50304, 1024, 1024, 16, 24, 4096, 64, 16),
+    "gpt1p3b": (50304, 2048, 2048, 16, 24, 8192, 32, 4),
+}
+
+
+# ----------------------------------------------------------------------------- tensor-parallel pieces
+class _GatherRows(torch.autograd.Function):
+    """all-gather rows forward, reduce-scatter rows backward (sequence-parallel boundary)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        out = torch.empty((x.shape[0] * W, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group)
+        out = torch.empty((g.shape[0] // W, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None
+
+
+class _ScatterRows(torch.autograd.Function):
+    """reduce-scatter rows forward, all-gather rows backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        out = torch.empty((x.shape[0] // W, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group)
+        out = torch.empty((g.shape[0] * W, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None
+
+
+class Block(nn.Module):
+    def __init__(self, d, heads, ff, tp=1, group=None):
+        super().__init__()
+        self.tp, self.group, self.h_local, self.dk = tp, group, heads // tp, d // heads
+        self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+        self.qkv = nn.Linear(d, 3 * d // tp)
+        self.proj = nn.Linear(d // tp, d)
+        self.fc1 = nn.Linear(d, ff // tp)
+        self.fc2 = nn.Linear(ff // tp, d)
+
+    def forward(self, x, B, S):
+        # x: [T_local, d] (T_local = B*S/tp rows when tensor parallel)
+        h = self.ln1(x)
+        if self.tp > 1:
+            h = _GatherRows.apply(h, self.group)
+        q, k, v = self.qkv(h).view(B, S, 3, self.h_local, self.dk).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B * S, -1)
+        a = F.linear(a, self.proj.weight)
+        if self.tp > 1:
+            a = _ScatterRows.apply(a, self.group)
+        x = x + a + self.proj.bias
+        h = self.ln2(x)
+        if self.tp > 1:
+            h = _GatherRows.apply(h, self.group)
+        h = F.linear(F.gelu(self.fc1(h), approximate="tanh"), self.fc2.weight)
+        if self.tp > 1:
+            h = _ScatterRows.apply(h, self.group)
+        return x + h + self.fc2.bias
+
+
+class GPT(nn.Module):
+    def __init__(self, vocab, seq, d, heads, layers, ff, tp=1, group=None):
+        super().__init__()
+        self.tp, self.group = tp, group
+        self.tok, self.pos = nn.Embedding(vocab, d), nn.Embedding(seq, d)
+        self.blocks = nn.ModuleList([Block(d, heads, ff, tp, group) for _ in range(layers)])
+        self.ln_f = nn.LayerNorm(d)
+
+    def forward(self, ids, targets):
+        B, S = ids.shape
+        pos = torch.arange(S, device=ids.device).repeat(B)
+        flat, tg = ids.reshape(-1), targets
+        if self.tp > 1:
+            r, W = dist.get_rank(self.group), self.tp
+            rows = B * S // W
+            flat, pos, tg = flat[r * rows:(r + 1) * rows], pos[r * rows:(r + 1) * rows], targets[r * rows:(r + 1) * rows]
+        x = self.tok(flat) + self.pos(pos)
+        for b in self.blocks:
+            x = b(x, B, S)
+        logits = F.linear(self.ln_f(x), self.tok.weight)
+        loss = F.cross_entropy(logits.float(), tg)
+        return loss / self.tp if self.tp > 1 else loss
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="gpt350m")
+    ap.add_argument("--parallel", default="dp")
+    ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    V, S, d, H, L, ff, gbatch, micro = CONFIGS[a.config]
+    micro = a.micro_batch or micro
+    tp = 1
+    if a.parallel.startswith("tp"):
+        spec = a.parallel[2:]
+        tp = int(spec.split("dp")[0])
+    dp = world // tp
+    tp_group = dp_group = None
+    if tp > 1 and world > 1:
+        for g in range(dp):
+            grp = dist.new_group(list(range(g * tp, (g + 1) * tp)))
+            if rank // tp == g:
+                tp_group = grp
+        for t in range(tp):
+            grp = dist.new_group(list(range(t, world, tp)))
+            if rank % tp == t:
+                dp_group = grp
+    torch.manual_seed(0)
+    model = GPT(V, S, d, H, L, ff, tp, tp_group).to(dev)
+    params = list(model.parameters())
+    opt = torch.optim.AdamW(params, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    ddp = None
+    if tp == 1 and world > 1:
+        ddp = nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
+    fwd = ddp if ddp is not None else model
+    per_replica = gbatch // dp
+    micro = min(micro, per_replica)
+    n_micro = per_replica // micro
+    replicated = [p for n, p in model.named_parameters() if tp > 1 and ("ln" in n or "tok" in n or "pos" in n or n.endswith("proj.bias") or n.endswith("fc2.bias"))]
+    ids_h = torch.randint(0, V, (per_replica, S)).pin_memory()
+    tgt_h = torch.randint(0, V, (per_replica * S,)).pin_memory()
+
+    def step():
+        ids, tgt = ids_h.to(dev, non_blocking=True), tgt_h.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        total = 0.0
+        for i in range(n_micro):
+            import contextlib
+            sync = ddp.no_sync() if (ddp is not None and i < n_micro - 1) else contextlib.nullcontext()
+            with sync, torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = fwd(ids[i * micro:(i + 1) * micro], tgt[i * micro * S:(i + 1) * micro * S]) / n_micro
+            with sync:
+                loss.backward()
+            total = total + loss.detach()
+        if tp > 1:
+            for p in replicated:
+                dist.all_reduce(p.grad, group=tp_group)
+            if dp > 1:
+                for p in params:
+                    dist.all_reduce(p.grad, op=dist.ReduceOp.AVG, group=dp_group)
+        opt.step()
+        return float(total.item())
+
+    for _ in range(a.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    if rank == 0:
+        print(json.dumps({"metric": "train tokens/sec (device-timed, max over ranks)", "impl": "pytorch nccl+cublas baseline",
+                          "value": gbatch * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+                          "warmup": a.warmup, "ms_per_step": ms, "dtype": "bf16 autocast, fp32 parameters",
+                          "loss_last": loss, "hbm_peak_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+                          "config": {"model": a.config, "global_batch": gbatch, "seq_len": S, "micro_batch": micro,
+                                     "parallelism": a.parallel if tp > 1 else f"dp{world}"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,74 @@
 
 namespace dg {
 
+// One 8-element vector: fp32 gradient sum -> optimizer on the master slice -> bf16 push to all ranks.
+struct OptState {   // master weights and Adam moments of one 8-element vector
+  float4 p0, p1, m0, m1, v0, v1;
+};
+__device__ __forceinline__ OptState load_state(const dg_rs_optim_args& a, int64_t e0) {
+  OptState s;
+  s.p0 = *reinterpret_cast<const float4*>(a.master + e0);
+  s.p1 = *reinterpret_cast<const float4*>(a.master + e0 + 4);
+  if (a.optimizer == 0) {
+    s.m0 = *reinterpret_cast<const float4*>(a.m + e0); s.m1 = *reinterpret_cast<const float4*>(a.m + e0 + 4);
+    s.v0 = *reinterpret_cast<const float4*>(a.v + e0); s.v1 = *reinterpret_cast<const float4*>(a.v + e0 + 4);
+  } else {
+    s.m0 = s.m1 = s.v0 = s.v1 = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  return s;
+}
+
+__device__ __forceinline__ void update_and_push(const dg_rs_optim_args& a, int64_t e0, int64_t base, const float (&acc)[8],
+                                                const OptState& st, float bc1, float bc2) {
+  const int W = a.world;
+  const float4 p0 = st.p0, p1 = st.p1;
+  float pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+  if (a.optimizer == 0) {
+    const float4 m0 = st.m0, m1 = st.m1, v0 = st.v0, v1 = st.v1;
+    float mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float g = acc[k] * a.grad_scale;
+      mw[k] = a.beta1 * mw[k] + (1.f - a.beta1) * g;
+      vw[k] = a.beta2 * vw[k] + (1.f - a.beta2) * g * g;
+      pw[k] -= a.lr * ((mw[k] / bc1) / (sqrtf(vw[k] / bc2) + a.eps) + a.wd * pw[k]);
+    }
+    *reinterpret_cast<float4*>(a.m + e0) = make_float4(mw[0], mw[1], mw[2], mw[3]);
+    *reinterpret_cast<float4*>(a.m + e0 + 4) = make_float4(mw[4], mw[5], mw[6], mw[7]);
+    *reinterpret_cast<float4*>(a.v + e0) = make_float4(vw[0], vw[1], vw[2], vw[3]);
+    *reinterpret_cast<float4*>(a.v + e0 + 4) = make_float4(vw[4], vw[5], vw[6], vw[7]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) pw[k] -= a.lr * a.grad_scale * acc[k];
+  }
+  *reinterpret_cast<float4*>(a.master + e0) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+  *reinterpret_cast<float4*>(a.master + e0 + 4) = make_float4(pw[4], pw[5], pw[6], pw[7]);
+  uint4 outv;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(pw[2 * k], pw[2 * k + 1]);
+  for (int rr = 0; rr < W; ++rr) {
+    const int r = (a.rank + rr) % W;  // start with the local copy, then rotate over peers
+    bf16* dst = reinterpret_cast<bf16*>(a.param_ptrs[r]) + base + e0;
+    if (r == a.rank) *reinterpret_cast<uint4*>(dst) = outv;
+    else peer::st_peer_16(dst, outv);
+  }
+}
+
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& raw) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float2 f = __bfloat1622float2(h[k]);
+    acc[2 * k] += f.x; acc[2 * k + 1] += f.y;
+  }
+}
+
+// WT = compile-time world size (0: any size, one vector at a time); U = vectors per thread and
+// iteration. All loads of an iteration (U*96 bytes of optimizer state from HBM, WT*U*16 bytes of
+// gradients over NVLink) are issued before the first is used.
+template <int WT, int U>
 __global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
   __shared__ int s_ok;
   const int W = a.world;
@@ -47,55 +115,47 @@ __global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
     const int64_t nvec = a.shard_n / 8;  // shard_n is a multiple of 8 (16-byte slices)
     const int64_t base = a.bucket_off + (int64_t)a.rank * a.shard_n;
     const float bc1 = 1.f - powf(a.beta1, (float)a.step), bc2 = 1.f - powf(a.beta2, (float)a.step);
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t e0 = v * 8;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      // 2. pull + reduce in rank order
-      for (int r = 0; r < W; ++r) {
-        const bf16* src = reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base + e0;
-        uint4 raw = (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : peer::ld_peer_16(src);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = __bfloat1622float2(h[k]);
-          acc[2 * k] += f.x; acc[2 * k + 1] += f.y;
+    if constexpr (WT == 0) {
+      for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e0 = v * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < W; ++r) {   // 2. pull + reduce in rank order
+          const bf16* src = reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base + e0;
+          add_bf16x8(acc, (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : peer::ld_peer_16(src));
         }
+        update_and_push(a, e0, base, acc, load_state(a, e0), bc1, bc2);   // 3. + 4.
       }
-      // 3. optimizer on the fp32 master slice
-      float4 p0 = *reinterpret_cast<const float4*>(a.master + e0), p1 = *reinterpret_cast<const float4*>(a.master + e0 + 4);
-      float pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-      if (a.optimizer == 0) {
-        float4 m0 = *reinterpret_cast<const float4*>(a.m + e0), m1 = *reinterpret_cast<const float4*>(a.m + e0 + 4);
-        float4 v0 = *reinterpret_cast<const float4*>(a.v + e0), v1 = *reinterpret_cast<const float4*>(a.v + e0 + 4);
-        float mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-        float vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    } else {
+      const bf16* srcs[WT];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          float g = acc[k] * a.grad_scale;
-          mw[k] = a.beta1 * mw[k] + (1.f - a.beta1) * g;
-          vw[k] = a.beta2 * vw[k] + (1.f - a.beta2) * g * g;
-          pw[k] -= a.lr * ((mw[k] / bc1) / (sqrtf(vw[k] / bc2) + a.eps) + a.wd * pw[k]);
+      for (int r = 0; r < WT; ++r) srcs[r] = reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base;
+      const int64_t tile = (int64_t)blockDim.x * U;
+      for (int64_t t0 = (int64_t)blockIdx.x * tile; t0 < nvec; t0 += (int64_t)gridDim.x * tile) {
+        // local optimizer state first, then the peer gradients: everything of this iteration is in
+        // flight together (HBM and NVLink latencies overlap instead of adding up)
+        OptState st[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
+          st[u] = load_state(a, (v < nvec ? v : 0) * 8);
         }
-        *reinterpret_cast<float4*>(a.m + e0) = make_float4(mw[0], mw[1], mw[2], mw[3]);
-        *reinterpret_cast<float4*>(a.m + e0 + 4) = make_float4(mw[4], mw[5], mw[6], mw[7]);
-        *reinterpret_cast<float4*>(a.v + e0) = make_float4(vw[0], vw[1], vw[2], vw[3]);
-        *reinterpret_cast<float4*>(a.v + e0 + 4) = make_float4(vw[4], vw[5], vw[6], vw[7]);
-      } else {
+        uint4 raw[U][WT];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) pw[k] -= a.lr * a.grad_scale * acc[k];
-      }
-      *reinterpret_cast<float4*>(a.master + e0) = make_float4(pw[0], pw[1], pw[2], pw[3]);
-      *reinterpret_cast<float4*>(a.master + e0 + 4) = make_float4(pw[4], pw[5], pw[6], pw[7]);
-      // 4. push the bf16 slice to every rank's parameter buffer
-      uint4 outv;
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&outv);
+        for (int u = 0; u < U; ++u) {
+          const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(pw[2 * k], pw[2 * k + 1]);
-      for (int rr = 0; rr < W; ++rr) {
-        const int r = (a.rank + rr) % W;  // start with the local copy, then rotate over peers
-        bf16* dst = reinterpret_cast<bf16*>(a.param_ptrs[r]) + base + e0;
-        if (r == a.rank) *reinterpret_cast<uint4*>(dst) = outv;
-        else peer::st_peer_16(dst, outv);
+          for (int r = 0; r < WT; ++r)
+            raw[u][r] = v < nvec ? peer::ld_peer_16(srcs[r] + v * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
+          if (v >= nvec) continue;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < WT; ++r) add_bf16x8(acc, raw[u][r]);   // fixed rank order: deterministic
+          update_and_push(a, v * 8, base, acc, st[u], bc1, bc2);
+        }
       }
     }
   }
@@ -140,10 +200,17 @@ extern "C" int dg_rs_optim(const dg_rs_optim_args* a, cudaStream_t stream) {
   dg_rs_optim_args args = *a;
   if (args.wait_cycles <= 0) args.wait_cycles = dg::peer::kFlagWaitCycles;
   int64_t nvec = a->shard_n / 8;
-  int64_t want = (nvec + 256 * 4 - 1) / (256 * 4);
+  const int U = a->world >= 4 ? 2 : 4;
+  int64_t want = (nvec + 256 * U - 1) / (256 * U);
   int cap = a->max_ctas > 0 ? a->max_ctas : 148 * 2;
   int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-  dg::rs_optim_kernel<<<blocks, 256, 0, stream>>>(args);
+  switch (a->world) {
+    case 1: dg::rs_optim_kernel<1, 4><<<blocks, 256, 0, stream>>>(args); break;
+    case 2: dg::rs_optim_kernel<2, 4><<<blocks, 256, 0, stream>>>(args); break;
+    case 4: dg::rs_optim_kernel<4, 2><<<blocks, 256, 0, stream>>>(args); break;
+    case 8: dg::rs_optim_kernel<8, 2><<<blocks, 256, 0, stream>>>(args); break;
+    default: dg::rs_optim_kernel<0, 1><<<blocks, 256, 0, stream>>>(args); break;
+  }
   DG_CHECK_LAUNCH();
   return DG_OK;
 }

@@ -91,6 +91,10 @@ int dg_reduce_rows(int dtype, void* out, void* mean_out, const void* x, int64_t 
 int64_t dg_reduce_cols_scratch_bytes(int64_t B, int64_t R, int64_t C);
 int dg_reduce_cols(int dtype, void* out, void* mean_out, const void* x, int64_t B, int64_t R,
                    int64_t C, int mode, void* scratch, cudaStream_t stream);
+// out[i] = scale * sum over s of partial[s * n + i] (+ residual[i]); fp32 partials (split-K
+// products) folded in a fixed order into an fp32 or bf16 result. n must be a multiple of 4.
+int dg_fold_partials(int out_dtype, void* out, const float* partial, const void* residual, int64_t n, int splits,
+                     float scale, cudaStream_t stream);
 // full sum -> out[1] (dtype of x, fp32 accumulate, fixed order); scratch >= 1024 floats.
 int dg_sum_all(int dtype, void* out, const void* x, int64_t n, float scale, void* scratch,
                cudaStream_t stream);

@@ -3,7 +3,9 @@
 // eps inside the sqrt, per-feature affine y = xhat * gamma[j] + beta[j] (the in-bounds
 // reading of src/cool_ops.h:41-46). mean and rstd are saved in fp32 for the backward.
 //   fwd : one warp per row, 16-byte loads, row cached in registers when d <= 32*8*VN
-//   bwd : (1) dx, one warp per row; (2) dgamma/dbeta as a split column reduction through scratch
+//   bwd : one fused kernel (dx + dgamma/dbeta, every input read once) for 16-byte aligned rows of up
+//         to 2048 bf16 / 1024 fp32 elements; otherwise (1) dx, one warp per row, and (2) dgamma/dbeta
+//         as a split column reduction through scratch
 #include "common.cuh"
 
 namespace dg {
@@ -151,6 +153,193 @@ __global__ void __launch_bounds__(256) layernorm_bwd_param_fold_kernel(T* __rest
   }
 }
 
+constexpr int kLnGroup = 16;               // CTAs per first-level fold group
+constexpr int kLnCountersPerLaunch = 32;   // 1 + groups (at most 296 / 16 = 19)
+constexpr int kLnLaunchSlots = 64;         // rolling window of launches that may be in flight
+__device__ unsigned int g_ln_counters[kLnLaunchSlots * kLnCountersPerLaunch];
+
+// Returns true in every thread of the CTA that arrives last of `expected`; resets the counter.
+__device__ __forceinline__ bool ln_arrive_last(unsigned int* counter, unsigned expected, int* s_flag) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(counter, 1u);
+    *s_flag = prev == expected - 1;
+    if (*s_flag) *counter = 0u;
+  }
+  __syncthreads();
+  const bool last = *s_flag != 0;
+  if (last) __threadfence();
+  return last;
+}
+
+// dst[0 .. 2d) = sum over `count` rows of src (row stride 2d floats), four rows in flight per thread in
+// interleaved chains. Writes fp32 to dst_f, or typed dgamma (first d) / dbeta (second d).
+template <typename T>
+__device__ __forceinline__ void ln_fold(float* dst_f, T* dgamma, const float* src, int count, int d, T* dbeta = nullptr) {
+  const int n2 = 2 * d;
+  for (int i = threadIdx.x * 4; i < n2; i += blockDim.x * 4) {
+    float4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* pp = src + i;
+    int b = 0;
+    for (; b + 4 <= count; b += 4) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + (int64_t)(b + j) * n2));
+        t[j].x += u.x; t[j].y += u.y; t[j].z += u.z; t[j].w += u.w;
+      }
+    }
+    for (; b < count; ++b) {
+      const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + (int64_t)b * n2));
+      t[0].x += u.x; t[0].y += u.y; t[0].z += u.z; t[0].w += u.w;
+    }
+    const float r[4] = {(t[0].x + t[1].x) + (t[2].x + t[3].x), (t[0].y + t[1].y) + (t[2].y + t[3].y),
+                        (t[0].z + t[1].z) + (t[2].z + t[3].z), (t[0].w + t[1].w) + (t[2].w + t[3].w)};
+    if (dst_f) {
+      *reinterpret_cast<float4*>(dst_f + i) = make_float4(r[0], r[1], r[2], r[3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = i + e;
+        if (c < d) stf(dgamma, c, r[e]);
+        else stf(dbeta, c - d, r[e]);
+      }
+    }
+  }
+}
+
+// Fused backward, one launch: one warp per row with the row of x and g held in registers (each
+// read once, 16-byte loads); the lane that owns a column also accumulates that column's dgamma and
+// dbeta over all rows of its warp. The eight warps of a CTA are added in warp order through shared
+// memory, every CTA writes one partial row pair to scratch, and the partials are folded in two
+// levels by the CTAs that arrive last (device counters) in a fixed order - deterministic.
+// KV = 16-byte vectors per lane (row length up to 32 * KV * VN).
+
+template <typename T, int KV>
+__global__ void __launch_bounds__(256, (KV <= 4 ? 2 : 1))
+layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __restrict__ dbeta, float* __restrict__ partial,
+                           const T* __restrict__ g, const T* __restrict__ x, const T* __restrict__ gamma,
+                           const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int d,
+                           unsigned int counter_idx) {
+  constexpr int VN = Vec16<T>::N;
+  extern __shared__ float s_acc[];   // [2][d]
+  __shared__ int s_last;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nvec = d / VN;
+  float adg[KV][VN], adb[KV][VN];
+#pragma unroll
+  for (int k = 0; k < KV; ++k)
+#pragma unroll
+    for (int e = 0; e < VN; ++e) { adg[k][e] = 0.f; adb[k][e] = 0.f; }
+
+  const int64_t warp = (int64_t)blockIdx.x * 8 + wid, nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const T* xr = x + row * d;
+    const T* gr = g + row * d;
+    Vec16<T> xv[KV], gv[KV];
+#pragma unroll
+    for (int k = 0; k < KV; ++k) {
+      const int v = lane + 32 * k;
+      if (v < nvec) { xv[k].load(xr + v * VN); gv[k].load(gr + v * VN); }
+    }
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < KV; ++k) {
+      const int v = lane + 32 * k;
+      if (v < nvec) {
+        float xf[VN], gf[VN], gm[VN];
+        xv[k].unpack(xf); gv[k].unpack(gf);
+        Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          const float xh = (xf[e] - mu) * rs, gh = gf[e] * gm[e];
+          s1 += gh; s2 += gh * xh;
+          adg[k][e] += gf[e] * xh; adb[k][e] += gf[e];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / (float)d;
+    s2 = warp_sum(s2) / (float)d;
+    if (dx) {
+      T* o = dx + row * d;
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        const int v = lane + 32 * k;
+        if (v < nvec) {
+          float xf[VN], gf[VN], gm[VN], of[VN];
+          xv[k].unpack(xf); gv[k].unpack(gf);
+          Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) {
+            const float xh = (xf[e] - mu) * rs;
+            of[e] = rs * (gf[e] * gm[e] - s1 - xh * s2);
+          }
+          t.pack(of); t.store(o + v * VN);
+        }
+      }
+    }
+  }
+  if (!dgamma) return;
+
+  // CTA: add the warps in warp order
+  for (int w = 0; w < 8; ++w) {
+    if (wid == w) {
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        const int v = lane + 32 * k;
+        if (v < nvec) {
+#pragma unroll
+          for (int e = 0; e < VN; ++e) {
+            const int c = v * VN + e;
+            if (w == 0) { s_acc[c] = adg[k][e]; s_acc[d + c] = adb[k][e]; }
+            else { s_acc[c] += adg[k][e]; s_acc[d + c] += adb[k][e]; }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // Two-level fold through scratch: the CTA that arrives last in its group of kLnGroup CTAs adds the
+  // group's partials (in CTA order) into one group partial; the group that finishes last adds the
+  // group partials (in group order) into dgamma/dbeta. Grouping and order are fixed: deterministic.
+  const int n2 = 2 * d;
+  float* mine = partial + (int64_t)blockIdx.x * n2;
+  for (int i = threadIdx.x; i < n2; i += blockDim.x) mine[i] = s_acc[i];
+  const unsigned group = blockIdx.x / kLnGroup, ngroups = (gridDim.x + kLnGroup - 1) / kLnGroup;
+  const unsigned gfirst = group * kLnGroup;
+  const unsigned gsize = gridDim.x - gfirst < (unsigned)kLnGroup ? gridDim.x - gfirst : (unsigned)kLnGroup;
+  unsigned int* counters = g_ln_counters + counter_idx * kLnCountersPerLaunch;
+  float* gpartial = partial + (int64_t)gridDim.x * n2;
+  if (!ln_arrive_last(counters + 1 + group, gsize, &s_last)) return;
+  ln_fold<float>(gpartial + (int64_t)group * n2, nullptr, partial + (int64_t)gfirst * n2, (int)gsize, d);
+  if (!ln_arrive_last(counters, ngroups, &s_last)) return;
+  ln_fold<T>(nullptr, dgamma, gpartial, (int)ngroups, d, dbeta);
+}
+
+template <typename T, int KV>
+static int launch_ln_bwd_fused(void* dx, void* dgamma, void* dbeta, const void* g, const void* x, const void* gamma,
+                               const float* mean, const float* rstd, int64_t rows, int64_t d, void* scratch, int grid,
+                               cudaStream_t stream) {
+  static unsigned int next_counter = 0;
+  const unsigned int idx = next_counter;
+  next_counter = (next_counter + 1) % kLnLaunchSlots;
+  const size_t smem = (size_t)2 * d * sizeof(float);
+  layernorm_bwd_fused_kernel<T, KV><<<grid, 256, smem, stream>>>((T*)dx, (T*)dgamma, (T*)dbeta, (float*)scratch, (const T*)g,
+                                                                 (const T*)x, (const T*)gamma, mean, rstd, rows, (int)d, idx);
+  DG_CHECK_LAUNCH();
+  return DG_OK;
+}
+
+static inline int ln_fused_grid(int64_t rows, int kv) {
+  // one warp per row, at least two rows per warp
+  const int64_t cap = 148 * (kv <= 4 ? 2 : 1);
+  const int64_t want = (rows + 15) / 16;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
 static inline int ln_splits(int64_t rows, int64_t d) {
   int64_t cb = (d + 31) / 32;
   int64_t want = (148 * 4 + cb - 1) / cb;
@@ -182,6 +371,16 @@ template <typename T>
 int launch_ln_bwd(void* dx, void* dgamma, void* dbeta, const void* g, const void* x, const void* gamma,
                   const float* mean, const float* rstd, int64_t rows, int64_t d, void* scratch,
                   cudaStream_t stream) {
+  constexpr int VN = Vec16<T>::N;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (dgamma && dbeta && d % VN == 0 && d / VN <= 32 * 8 && al(x) && al(g) && al(gamma) && (!dx || al(dx))) {
+    const int kv = (int)((d / VN + 31) / 32);
+    const int grid = ln_fused_grid(rows, kv <= 1 ? 1 : kv <= 2 ? 2 : kv <= 4 ? 4 : 8);
+    if (kv <= 1) return launch_ln_bwd_fused<T, 1>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
+    if (kv <= 2) return launch_ln_bwd_fused<T, 2>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
+    if (kv <= 4) return launch_ln_bwd_fused<T, 4>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
+    return launch_ln_bwd_fused<T, 8>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
+  }
   int blocks = grid_for(rows, 8);
   if (dx) {
     layernorm_bwd_dx_kernel<T><<<blocks, 256, 0, stream>>>((T*)dx, (const T*)g, (const T*)x, (const T*)gamma, mean,
@@ -215,7 +414,9 @@ extern "C" int dg_layernorm_fwd(int dtype, void* y, float* mean, float* rstd, co
 
 extern "C" int64_t dg_layernorm_bwd_scratch_bytes(int64_t rows, int64_t d) {
   if (rows <= 0 || d <= 0) return 0;
-  return (int64_t)sizeof(float) * 2 * d * dg::ln_splits(rows, d);
+  const int64_t split = (int64_t)sizeof(float) * 2 * d * dg::ln_splits(rows, d);
+  const int64_t fused = (int64_t)sizeof(float) * 2 * d * (148 * 2 + 32);   // one partial row pair per CTA + per group
+  return split > fused ? split : fused;
 }
 
 extern "C" int dg_layernorm_bwd(int dtype, void* dx, void* dgamma, void* dbeta, const void* g, const void* x,

@@ -114,6 +114,114 @@ __global__ void __launch_bounds__(256) reduce_cols_partial_vec_kernel(float* __r
   }
 }
 
+// One-launch column sum / mean: every CTA writes the partial sums of its row split, and the CTA
+// that arrives last for a column block (device counter, reset by that CTA) folds the S partials
+// in split order - the result does not depend on which CTA is last, so it stays deterministic.
+constexpr int kColsCounters = 8192;
+__device__ unsigned int g_cols_counters[kColsCounters];
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_fused_kernel(T* __restrict__ out, float* __restrict__ partial,
+                                                                const T* __restrict__ x, int64_t R, int64_t C,
+                                                                int64_t rows_per_split, int S, float scale,
+                                                                unsigned int counter_base) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float sh[8][32 * VN + 1];
+  __shared__ int s_last;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z, s = blockIdx.y;
+  const int64_t c0 = ((int64_t)blockIdx.x * 32 + tx) * VN;
+  const int64_t r0 = s * rows_per_split;
+  int64_t r1 = r0 + rows_per_split;
+  if (r1 > R) r1 = R;
+  float acc[VN];
+#pragma unroll
+  for (int k = 0; k < VN; ++k) acc[k] = 0.f;
+  if (c0 < C) {
+    const T* p = x + b * R * C + c0;
+    int64_t r = r0 + ty;
+    for (; r + 8 < r1; r += 16) {   // two independent 16-byte loads in flight per thread
+      Vec16<T> t0, t1; t0.load(p + r * C); t1.load(p + (r + 8) * C);
+      float f0[VN], f1[VN]; t0.unpack(f0); t1.unpack(f1);
+#pragma unroll
+      for (int k = 0; k < VN; ++k) acc[k] += f0[k] + f1[k];
+    }
+    for (; r < r1; r += 8) {
+      Vec16<T> t; t.load(p + r * C);
+      float f[VN]; t.unpack(f);
+#pragma unroll
+      for (int k = 0; k < VN; ++k) acc[k] += f[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VN; ++k) sh[ty][tx * VN + k] = acc[k];
+  __syncthreads();
+  const int64_t cb = (int64_t)blockIdx.x * 32 * VN;
+  for (int i = threadIdx.x; i < 32 * VN; i += blockDim.x) {
+    const int64_t c = cb + i;
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += sh[k][i];
+      if (S == 1) stf(out, b * C + c, t * scale);
+      else partial[(b * S + s) * C + c] = t;
+    }
+  }
+  if (S == 1) return;
+  __threadfence();
+  __syncthreads();
+  unsigned int* counter = g_cols_counters + (counter_base + (unsigned)(b * gridDim.x + blockIdx.x)) % kColsCounters;
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(counter, 1u);
+    s_last = prev == (unsigned)S - 1u;
+    if (s_last) *counter = 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < 32 * VN; i += blockDim.x) {
+    const int64_t c = cb + i;
+    if (c < C) {
+      // four interleaved chains (k mod 4) keep four loads in flight; the grouping is fixed, so the
+      // sum is the same on every run
+      float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+      const float* pp = partial + b * S * C + c;
+      int k = 0;
+      for (; k + 4 <= S; k += 4) {
+        t0 += __ldcg(pp + (int64_t)k * C); t1 += __ldcg(pp + (int64_t)(k + 1) * C);
+        t2 += __ldcg(pp + (int64_t)(k + 2) * C); t3 += __ldcg(pp + (int64_t)(k + 3) * C);
+      }
+      for (; k < S; ++k) t0 += __ldcg(pp + (int64_t)k * C);
+      stf(out, b * C + c, ((t0 + t1) + (t2 + t3)) * scale);
+    }
+  }
+}
+
+// out[i] = scale * sum_s partial[s, i]: folds split-K partial products (fixed order) into any dtype.
+template <typename T>
+__global__ void __launch_bounds__(256) fold_partials_kernel(T* __restrict__ out, const float* __restrict__ partial,
+                                                            const T* __restrict__ residual, int64_t n, int S,
+                                                            float scale) {
+  const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n) return;
+  if (i4 + 4 <= n) {
+    float4 t = *reinterpret_cast<const float4*>(partial + i4);
+    for (int s = 1; s < S; ++s) {
+      const float4 u = *reinterpret_cast<const float4*>(partial + (int64_t)s * n + i4);
+      t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+    }
+    float v[4] = {t.x * scale, t.y * scale, t.z * scale, t.w * scale};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) stf(out, i4 + k, v[k] + (residual ? ldf(residual, i4 + k) : 0.f));
+  } else {
+    for (int64_t i = i4; i < n; ++i) {
+      float t = 0.f;
+      for (int s = 0; s < S; ++s) t += partial[(int64_t)s * n + i];
+      stf(out, i, t * scale + (residual ? ldf(residual, i) : 0.f));
+    }
+  }
+}
+
 // Stage 2: fold the S partials. post: 0 -> scale*sum into T out; 1 -> sqrt(scale*sum); also optional fp32 copy.
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_cols_fold_kernel(T* __restrict__ out, float* __restrict__ out_f32,
@@ -156,7 +264,7 @@ __global__ void __launch_bounds__(256) sum_all_fold_kernel(T* __restrict__ out, 
 
 static inline int cols_splits(int64_t B, int64_t R, int64_t C) {
   int64_t col_blocks = (C + 255) / 256;
-  int64_t want = (148 * 4 + B * col_blocks - 1) / (B * col_blocks);
+  int64_t want = (148 * 2 + B * col_blocks - 1) / (B * col_blocks);
   int64_t max_s = (R + 63) / 64;
   if (want > max_s) want = max_s;
   if (want < 1) want = 1;
@@ -179,6 +287,15 @@ int launch_reduce_cols(void* out, void* mean_out, const void* x, int64_t B, int6
     if (vec) reduce_cols_partial_vec_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, shift, R, C, rps, S, square);
     else reduce_cols_partial_kernel<T><<<grid, 256, 0, stream>>>(partial, (const T*)x, shift, R, C, rps, S, square);
   };
+  if ((mode == DG_RED_SUM || mode == DG_RED_MEAN) && vec && (int64_t)grid.x * B <= kColsCounters) {
+    static unsigned int next_counter = 0;   // rolling window over the counter pool: launches that can
+    const unsigned int base = next_counter; // be in flight together never share a counter
+    next_counter = (next_counter + grid.x * (unsigned)B) % kColsCounters;
+    reduce_cols_fused_kernel<T><<<grid, 256, 0, stream>>>((T*)out, partial, (const T*)x, R, C, rps, S,
+                                                          mode == DG_RED_SUM ? 1.f : 1.f / (float)R, base);
+    DG_CHECK_LAUNCH();
+    return DG_OK;
+  }
   stage1(nullptr, 0);
   DG_CHECK_LAUNCH();
   if (mode == DG_RED_SUM || mode == DG_RED_MEAN) {
@@ -229,6 +346,22 @@ extern "C" int dg_reduce_cols(int dtype, void* out, void* mean_out, const void* 
   if (dtype == DG_F32) return dg::launch_reduce_cols<float>(out, mean_out, x, B, R, C, mode, scratch, stream);
   if (dtype == DG_BF16) return dg::launch_reduce_cols<dg::bf16>(out, mean_out, x, B, R, C, mode, scratch, stream);
   return DG_ERR_BAD_ARG;
+}
+
+extern "C" int dg_fold_partials(int out_dtype, void* out, const float* partial, const void* residual, int64_t n,
+                                int splits, float scale, cudaStream_t stream) {
+  if (n <= 0) return DG_OK;
+  if (!out || !partial || splits < 1 || n % 4 != 0 || (reinterpret_cast<uintptr_t>(partial) & 15u)) return DG_ERR_BAD_ARG;
+  const int blocks = (int)((n / 4 + 255) / 256);
+  if (out_dtype == DG_F32)
+    dg::fold_partials_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, partial, (const float*)residual, n, splits, scale);
+  else if (out_dtype == DG_BF16)
+    dg::fold_partials_kernel<dg::bf16><<<blocks, 256, 0, stream>>>((dg::bf16*)out, partial, (const dg::bf16*)residual, n,
+                                                                  splits, scale);
+  else
+    return DG_ERR_BAD_ARG;
+  DG_CHECK_LAUNCH();
+  return DG_OK;
 }
 
 extern "C" int dg_sum_all(int dtype, void* out, const void* x, int64_t n, float scale, void* scratch,

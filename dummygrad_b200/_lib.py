@@ -77,6 +77,7 @@ _SIGS = {
     "dg_reduce_rows": [_i32, _vp, _vp, _vp, _i64, _i64, _i32, _vp],
     "dg_reduce_cols": [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp],
     "dg_sum_all": [_i32, _vp, _vp, _i64, _f32, _vp, _vp],
+    "dg_fold_partials": [_i32, _vp, _vp, _vp, _i64, _i32, _f32, _vp],
     "dg_softmax_fwd": [_i32, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _i64, _vp],
     "dg_softmax_bwd": [_i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _i64, _vp],
     "dg_layernorm_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp],

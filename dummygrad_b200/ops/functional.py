@@ -57,6 +57,17 @@ def _grad(grads, shape, dtype, device) -> torch.Tensor:
     return g
 
 
+def _sink(t: Tensor | None, dtype, numel: int) -> torch.Tensor | None:
+    """The gradient sink of leaf ``t`` when a backward node may write the complete gradient straight
+    into it (saves the copy into e.g. a data-parallel bucket), else None."""
+    if t is None or t.grad_fn is not None or not t.requires_grad:
+        return None
+    sk = t._grad_sink
+    if sk is None or t._sink_filled or sk.dtype != dtype or sk.numel() != numel or not sk.is_cuda:
+        return None
+    return t.claim_grad_sink()
+
+
 def _same_shape(a: Tensor, b: Tensor, what: str) -> None:
     if a.shape != b.shape:
         raise RuntimeError(f"{what}: shapes {a.shape} and {b.shape} differ")
@@ -967,11 +978,11 @@ class LinearBackward(Node):
     """Backward of y = act(x W + b) (+ residual): dgrad and wgrad GEMMs with operand layouts taken
     through descriptors (no transposes), activation derivative fused in the dgrad-side epilogue."""
 
-    def __init__(self, x2d, W, pre_act, act, has_bias, xshape, has_res, W_tensor):
+    def __init__(self, x2d, W, pre_act, act, has_bias, xshape, has_res, W_tensor, b_tensor=None):
         super().__init__()
         self.x2d, self.W, self.pre_act, self.act = x2d, W, pre_act, act
         self.has_bias, self.xshape, self.has_res = has_bias, xshape, has_res
-        self.W_tensor = W_tensor
+        self.W_tensor, self.b_tensor = W_tensor, b_tensor
 
     def apply(self, grads):
         W, x2d = self.W, self.x2d
@@ -981,10 +992,10 @@ class LinearBackward(Node):
         if self.act is not None:
             g = K.ew("GELU_BWD" if self.act == "gelu" else "RELU_BWD", g, self.pre_act)
         dx = K.gemm2d(g, W, trans_b=True).reshape(self.xshape)
-        dW = K.gemm2d(x2d, g, trans_a=True)
+        dW = K.gemm2d(x2d, g, trans_a=True, out=_sink(self.W_tensor, g.dtype, Kin * N))
         outs = [dx, dW]
         if self.has_bias:
-            db, _ = K.reduce_cols(g.reshape(1, g.shape[0], N), RED_SUM)
+            db, _ = K.reduce_cols(g.reshape(1, g.shape[0], N), RED_SUM, out=_sink(self.b_tensor, g.dtype, N))
             outs.append(db.reshape(1, N))
         if self.has_res:
             outs.append(gres.reshape(*self.xshape[:-1], N))
@@ -1012,20 +1023,22 @@ def linear(x: Tensor, W: Tensor, b: Tensor | None = None, act: str | None = None
                           device=xd.device)
     od = K.gemm2d(xd, Wd, bias=bd, epi=epi, aux=pre, residual=rd).reshape(*x.shape[:-1], N)
     inputs = [x, W] + ([b] if b is not None else []) + ([residual] if residual is not None else [])
-    return _result(od, lambda: LinearBackward(xd, Wd, pre, act, b is not None, tuple(x.shape), residual is not None, W),
+    return _result(od, lambda: LinearBackward(xd, Wd, pre, act, b is not None, tuple(x.shape), residual is not None, W, b),
                    inputs)
 
 
 class LayerNormBackward(Node):
-    def __init__(self, x, gamma, mean, rstd):
+    def __init__(self, x, gamma, mean, rstd, gamma_t=None, beta_t=None):
         super().__init__()
         self.x, self.gamma, self.mean, self.rstd = x, gamma, mean, rstd
+        self.gamma_t, self.beta_t = gamma_t, beta_t
 
     def apply(self, grads):
         x = self.x
-        g = _grad(grads, x.shape, x.dtype, x.device)
-        dx, dg, db = K.layernorm_bwd(g, x, self.gamma, self.mean, self.rstd)
         d = x.shape[-1]
+        g = _grad(grads, x.shape, x.dtype, x.device)
+        dx, dg, db = K.layernorm_bwd(g, x, self.gamma, self.mean, self.rstd,
+                                     dgamma_out=_sink(self.gamma_t, x.dtype, d), dbeta_out=_sink(self.beta_t, x.dtype, d))
         return [dx, dg.reshape(1, d), db.reshape(1, d)]
 
     def release_variables(self):
@@ -1039,7 +1052,7 @@ def layer_norm(x: Tensor, gamma: Tensor, beta: Tensor, eps: float = 1e-5) -> Ten
     xd = _c(x)
     gd, bd = _c(gamma).reshape(d), _c(beta).reshape(d)
     y, mu, rstd = K.layernorm_fwd(xd, gd, bd, eps)
-    return _result(y, lambda: LayerNormBackward(xd, gd, mu, rstd), (x, gamma, beta))
+    return _result(y, lambda: LayerNormBackward(xd, gd, mu, rstd, gamma, beta), (x, gamma, beta))
 
 
 class EmbeddingBackward(Node):
@@ -1203,19 +1216,22 @@ class MlpBackward(Node):
     """Backward of fc2(gelu(fc1(x))) (+ residual). The GELU derivative runs in the epilogue of the
     GEMM that produces dH, so the [tokens, d_ff] gradient is written once."""
 
-    def __init__(self, x2d, W1, W2, pre, h, xshape, has_res):
+    def __init__(self, x2d, W1, W2, pre, h, xshape, has_res, leaves=(None, None, None, None)):
         super().__init__()
         self.x2d, self.W1, self.W2, self.pre, self.h, self.xshape, self.has_res = x2d, W1, W2, pre, h, xshape, has_res
+        self.leaves = leaves     # (W1, b1, W2, b2) tensors, for writing gradients straight into their sinks
 
     def apply(self, grads):
         x2d, W1, W2 = self.x2d, self.W1, self.W2
         d_ff, d_out = W2.shape
         g = _grad(grads, (*self.xshape[:-1], d_out), x2d.dtype, x2d.device).reshape(-1, d_out)
-        dW2 = K.gemm2d(self.h, g, trans_a=True)
-        db2, _ = K.reduce_cols(g.reshape(1, g.shape[0], d_out), RED_SUM)
+        tW1, tb1, tW2, tb2 = self.leaves
+        dt = g.dtype
+        dW2 = K.gemm2d(self.h, g, trans_a=True, out=_sink(tW2, dt, d_ff * d_out))
+        db2, _ = K.reduce_cols(g.reshape(1, g.shape[0], d_out), RED_SUM, out=_sink(tb2, dt, d_out))
         dh = K.gemm2d(g, W2, trans_b=True, epi=L.EPI_DGELU, aux=self.pre)
-        dW1 = K.gemm2d(x2d, dh, trans_a=True)
-        db1, _ = K.reduce_cols(dh.reshape(1, dh.shape[0], d_ff), RED_SUM)
+        dW1 = K.gemm2d(x2d, dh, trans_a=True, out=_sink(tW1, dt, W1.shape[0] * d_ff))
+        db1, _ = K.reduce_cols(dh.reshape(1, dh.shape[0], d_ff), RED_SUM, out=_sink(tb1, dt, d_ff))
         dx = K.gemm2d(dh, W1, trans_b=True).reshape(self.xshape)
         outs = [dx, dW1, db1.reshape(1, d_ff), dW2, db2.reshape(1, d_out)]
         if self.has_res:
@@ -1237,4 +1253,5 @@ def mlp(x: Tensor, W1: Tensor, b1: Tensor, W2: Tensor, b2: Tensor, residual: Ten
     rd = _c(residual).reshape(-1, d_out) if residual is not None else None
     od = K.gemm2d(h, W2d, bias=_c(b2).reshape(d_out), residual=rd).reshape(*x.shape[:-1], d_out)
     inputs = [x, W1, b1, W2, b2] + ([residual] if residual is not None else [])
-    return _result(od, lambda: MlpBackward(xd, W1d, W2d, pre, h, tuple(x.shape), residual is not None), inputs)
+    return _result(od, lambda: MlpBackward(xd, W1d, W2d, pre, h, tuple(x.shape), residual is not None, (W1, b1, W2, b2)),
+                   inputs)

@@ -226,22 +226,30 @@ def reduce_rows(x: torch.Tensor, mode: int, want_mean: bool = False):
     return out, mean
 
 
-def reduce_cols(x: torch.Tensor, mode: int, want_mean: bool = False):
-    """x [B, R, C] contiguous -> [B, C]. Returns (out, mean or None)."""
+def reduce_cols(x: torch.Tensor, mode: int, want_mean: bool = False, out: torch.Tensor | None = None):
+    """x [B, R, C] contiguous -> [B, C] (written into ``out`` when given: same dtype, B*C elements,
+    contiguous). Returns (out, mean or None)."""
     B, R, Cc = x.shape
+    if out is not None:
+        assert out.dtype == x.dtype and out.numel() == B * Cc and out.is_contiguous()
     if not _is_cuda(x):
         xf = x.float()
         mu = xf.mean(dim=1)
         res = {RED_SUM: lambda: xf.sum(1), RED_MEAN: lambda: mu, RED_VAR: lambda: xf.var(1, unbiased=False),
                RED_STD: lambda: xf.var(1, unbiased=False).sqrt()}[mode]()
+        if out is not None:
+            out.copy_(res.to(x.dtype).reshape(out.shape))
+            res = out
         return res.to(x.dtype), (mu.to(x.dtype) if want_mean else None)
     lib = L.load()
-    out = torch.empty(B, Cc, dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty(B, Cc, dtype=x.dtype, device=x.device)
     mean = torch.empty(B, Cc, dtype=x.dtype, device=x.device) if (want_mean or mode >= RED_VAR) else None
     scratch = torch.empty(max(int(lib.dg_reduce_cols_scratch_bytes(B, R, Cc)), 4), dtype=torch.uint8, device=x.device)
     L.check(lib.dg_reduce_cols(L.dtype_code(x.dtype), out.data_ptr(), L.ptr(mean), x.data_ptr(), B, R, Cc, mode,
                                scratch.data_ptr(), L.stream_ptr()), "dg_reduce_cols")
-    _cnt(2 if mode <= RED_MEAN else 4)
+    vec = Cc % (8 if x.dtype == torch.bfloat16 else 4) == 0
+    _cnt((1 if vec else 2) if mode <= RED_MEAN else 4)
     return out, (mean if want_mean else None)
 
 
@@ -324,8 +332,9 @@ def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps:
     return y, mean, rstd
 
 
-def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True):
-    """Returns (dx or None, dgamma [d] or None, dbeta [d] or None)."""
+def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True, dgamma_out=None, dbeta_out=None):
+    """Returns (dx or None, dgamma [d] or None, dbeta [d] or None); the parameter gradients are
+    written into ``dgamma_out`` / ``dbeta_out`` (d contiguous elements of x's dtype) when given."""
     d = x.shape[-1]
     rows = x.numel() // d
     if not _is_cuda(x):
@@ -336,12 +345,19 @@ def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True):
         dx = rstd[:, None] * (gh - gh.mean(1, keepdim=True) - xh * (gh * xh).mean(1, keepdim=True))
         dg = (gf * xh).sum(0)
         db = gf.sum(0)
+        dg, db = dg.to(x.dtype), db.to(x.dtype)
+        if dgamma_out is not None:
+            dgamma_out.copy_(dg.reshape(dgamma_out.shape))
+            dg = dgamma_out
+        if dbeta_out is not None:
+            dbeta_out.copy_(db.reshape(dbeta_out.shape))
+            db = dbeta_out
         return (dx.reshape(x.shape).to(x.dtype) if need_dx else None,
-                dg.to(x.dtype) if need_dparams else None, db.to(x.dtype) if need_dparams else None)
+                dg if need_dparams else None, db if need_dparams else None)
     lib = L.load()
     dx = torch.empty_like(x) if need_dx else None
-    dgm = torch.empty(d, dtype=x.dtype, device=x.device) if need_dparams else None
-    dbt = torch.empty(d, dtype=x.dtype, device=x.device) if need_dparams else None
+    dgm = (dgamma_out if dgamma_out is not None else torch.empty(d, dtype=x.dtype, device=x.device)) if need_dparams else None
+    dbt = (dbeta_out if dbeta_out is not None else torch.empty(d, dtype=x.dtype, device=x.device)) if need_dparams else None
     scratch = None
     if need_dparams:
         scratch = torch.empty(max(int(lib.dg_layernorm_bwd_scratch_bytes(rows, d)), 4), dtype=torch.uint8,
@@ -349,7 +365,8 @@ def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True):
     L.check(lib.dg_layernorm_bwd(L.dtype_code(x.dtype), L.ptr(dx), L.ptr(dgm), L.ptr(dbt), g.data_ptr(), x.data_ptr(),
                                  gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d, L.ptr(scratch),
                                  L.stream_ptr()), "dg_layernorm_bwd")
-    _cnt((1 if need_dx else 0) + (2 if need_dparams else 0))
+    fused = need_dparams and d % (8 if x.dtype == torch.bfloat16 else 4) == 0 and d <= (2048 if x.dtype == torch.bfloat16 else 1024)
+    _cnt(1 if fused else (1 if need_dx else 0) + (2 if need_dparams else 0))
     return dx, dgm, dbt
 
 
@@ -585,6 +602,11 @@ def gemm2d(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, ou
             part = torch.empty(s, M, N, dtype=torch.float32, device=a.device)
             gemm2d(a.view(s, K // s, M), b.view(s, K // s, N), trans_a=True, out_dtype=torch.float32, alpha=alpha,
                    out=part)
+            if (M * N) % 4 == 0 and out.is_contiguous():
+                L.check(lib.dg_fold_partials(L.dtype_code(out.dtype), out.data_ptr(), part.data_ptr(), L.ptr(residual),
+                                             M * N, s, 1.0, L.stream_ptr()), "dg_fold_partials")
+                _cnt()
+                return out
             folded, _ = reduce_cols(part.view(1, s, M * N), RED_SUM)
             folded = folded.view(M, N)
             if residual is not None:

@@ -152,7 +152,9 @@ class AccumulateGrad(Node):
         sink = var._grad_sink
         if sink is not None:
             # pre-allocated gradient storage (e.g. a view into a data-parallel bucket)
-            if var._sink_filled:
+            if g.data_ptr() == sink.data_ptr():
+                pass    # the producing kernel wrote (or the engine summed) straight into the sink
+            elif var._sink_filled:
                 K.accumulate_(sink, K.contiguous(g))
             else:
                 K.assign_(sink, K.contiguous(g))
@@ -384,6 +386,16 @@ class Tensor:
         self._grad_sink = buf
         self._sink_filled = False
         self.grad = None
+
+    def claim_grad_sink(self) -> torch.Tensor | None:
+        """For backward nodes that can write a parameter gradient anywhere: the gradient sink, if this
+        leaf has one that holds nothing yet this step (the caller must then produce the COMPLETE
+        gradient contribution in it and return it as the gradient), else None. Claiming marks the
+        sink as filled, so a second use of the same parameter accumulates instead of overwriting."""
+        if self._grad_sink is None or self._sink_filled:
+            return None
+        self._sink_filled = True
+        return self._grad_sink
 
     # ------------------------------------------------------------------ backward
     def backward(self, retain_graph: bool = False) -> None:
