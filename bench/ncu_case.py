@@ -1,0 +1,83 @@
+"""Small, self-ending cases of the hot kernels for profiler captures (one GPU).
+
+    python bench/ncu_case.py --kernel gemm|gemm_gelu|wgrad|attn_fwd|attn_bwd|ln_bwd|xent|rs_adam
+
+Each case touches more than the L2 size but holds at most a few GB on the device, launches the
+kernel of interest three times after one warm-up and exits. Run it plainly first; capture with
+`ncu --set full --clock-control none -k regex:<kernel> -c 2 -o <file> python bench/ncu_case.py --kernel <name>`.
+"""
+import argparse
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import dummygrad_b200 as dg  # noqa: E402
+from dummygrad_b200 import _lib as L  # noqa: E402
+from dummygrad_b200.ops import kernels as K  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    bf = torch.bfloat16
+    rnd = lambda *s: (torch.randn(*s, device=dev) * 0.3).to(bf)
+    reps = 4
+    if a.kernel == "gemm":              # 16384 x 4096 x 4096: 0.55 TFLOP, 0.3 GB of operands
+        x, w = rnd(16384, 4096), rnd(4096, 4096)
+        fn = lambda: K.gemm2d(x, w)
+    elif a.kernel == "gemm_gelu":       # the fc1 shape of the 350M model with bias + GELU + saved pre-activation
+        x, w, b = rnd(65536, 1024), rnd(1024, 4096), rnd(4096)
+        pre = torch.empty(65536, 4096, dtype=bf, device=dev)
+        fn = lambda: K.gemm2d(x, w, bias=b, epi=L.EPI_GELU, aux=pre)
+    elif a.kernel == "wgrad":           # split-K weight gradient: [1024, 4096] = x^T g over 65536 rows
+        x, g = rnd(65536, 1024), rnd(65536, 4096)
+        fn = lambda: K.gemm2d(x, g, trans_a=True)
+    elif a.kernel in ("attn_fwd", "attn_bwd"):
+        B, H, S, dk = 16, 16, 1024, 64
+        q, k, v, go = (rnd(B, S, H * dk) for _ in range(4))
+        sc = 1.0 / math.sqrt(dk)
+        o, lse = K.attention_fwd(q, k, v, H, True, sc)
+        fn = (lambda: K.attention_fwd(q, k, v, H, True, sc)) if a.kernel == "attn_fwd" else \
+            (lambda: K.attention_bwd(q, k, v, o, go, lse, H, True, sc))
+    elif a.kernel == "ln_bwd":
+        x, g, gm = rnd(65536, 1024), rnd(65536, 1024), rnd(1024)
+        y, mu, rs = K.layernorm_fwd(x, gm, gm, 1e-5)
+        fn = lambda: K.layernorm_bwd(g, x, gm, mu, rs)
+    elif a.kernel == "xent":
+        lg = rnd(8192, 50304)
+        tg = torch.randint(0, 50304, (8192,), device=dev)
+        fn = lambda: K.xent_fwd_bwd(lg, tg, 1.0 / 8192)
+    elif a.kernel == "rs_adam":         # the fused reduce-scatter + AdamW kernel on one rank (64 M parameters)
+        from dummygrad_b200.parallel.dp import DataParallel
+
+        class Flat:
+            def __init__(self):
+                self.p = dg.Tensor([64 * 2 ** 20], True, dtype=bf, device=dev)
+
+            def parameters(self):
+                return [self.p]
+
+        dp = DataParallel(Flat(), lr=1e-3, comm="fused", bucket_mb=4096, max_comm_ctas=148)
+        dp.grad_flat.normal_()
+
+        def fn():
+            dp.begin_step()
+            for b in dp.buckets:
+                for p in b.params:
+                    p._sink_filled = True
+            dp.finish_step()
+    else:
+        raise SystemExit(f"unknown kernel {a.kernel}")
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    print(f"{a.kernel}: ok, status {K.gemm_status()}")
+
+
+if __name__ == "__main__":
+    main()
