@@ -19,7 +19,7 @@
 namespace dg {
 namespace sm100 {
 
-constexpr int kAttnBwdThreads = 320;   // TMA warp, MMA warp, 8 gradient warps (two per TMEM lane group)
+constexpr int kAttnBwdThreads = 448;   // TMA warp, MMA warp, 8 gradient warps (two per TMEM lane group), 4 dQ drain warps
 
 struct AttnBwdParams {
   const float* lse;
@@ -122,7 +122,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(kv_full, 1);
     for (int s = 0; s < STG; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(sdp_full, 1); mbar_init(s_free, 8); mbar_init(pds_ready, 256); mbar_init(pds_free, 1);
-    mbar_init(dq_full, 1); mbar_init(dq_free, 8); mbar_init(acc_full, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, 4); mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
@@ -221,10 +221,63 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) umma_commit(acc_full);
       else { if (p.status) atomicExch(p.status, 0x22); *abort_flag = 1; }
     }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ dQ drain warps (10..13), one per TMEM lane group
+    // They take each finished dQ_i partial out of TMEM, pack it as two [128 x 32] fp32 slabs
+    // (128-byte swizzle) and hand the slabs to the TMA unit, which adds them into the fp32
+    // accumulator in full 128-byte lines. Running this in its own warps lets the gradient warps
+    // start on the next tile while the MMAs of this one are still in flight.
+    const int lg = warp & 3;
+    const int r = lg * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(lg * 32) << 16;
+    const int sw = r & 7;
+    const bool issuer = (threadIdx.x == 320);
+    bool ok = true;
+    for (int n = 0; n < N; ++n) {
+      const int it = i0 + n;
+      ok = bounded_wait(dq_full, n & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int rd = 0; rd < DK / 64; ++rd) {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(tmem_base + lane_base + cDQ + rd * 32, ra);
+        tmem_ld_32x32(tmem_base + lane_base + cDQ + (DK / 64 + rd) * 32, rb);
+        tc_wait_ld();
+        if (issuer) bulk_wait_read0();            // the previous round's reduce has read its slabs
+        named_bar_sync(1, 128);
+        uint8_t* srow0 = sDQ + r * 128;
+        uint8_t* srow1 = sDQ + 16384 + r * 128;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          *reinterpret_cast<uint4*>(srow0 + ((q ^ sw) << 4)) = make_uint4(ra[q * 4], ra[q * 4 + 1], ra[q * 4 + 2], ra[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(srow1 + ((q ^ sw) << 4)) = make_uint4(rb[q * 4], rb[q * 4 + 1], rb[q * 4 + 2], rb[q * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(2, 128);
+        if (issuer) {
+          tma_reduce_add_4d(&tmDQ, sDQ, rd * 32, it * 128, h, b);
+          tma_reduce_add_4d(&tmDQ, sDQ + 16384, (DK / 64 + rd) * 32, it * 128, h, b);
+          bulk_commit();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+    }
+    if (!ok && lane == 0) {
+      if (p.status) atomicExch(p.status, 0x24);
+      *abort_flag = 1;
+    }
+    if (issuer) bulk_wait_all();                  // reduce-adds must have left shared memory
   } else {
     // ------------------------------------------------------------------ softmax-gradient warps (2..9)
     // Two warps share each TMEM lane group (= 32 query rows); they split the columns in halves.
     // Nothing is reduced along a row here (LSE and Delta are precomputed), so the split is free.
+    // Per tile: S and dP go from TMEM to registers (which frees the TMEM columns for the next
+    // tile's MMAs at once), P and dS are computed and packed to bf16 in registers, and only then the
+    // warp waits for the previous tile's MMAs to release the shared-memory operand tiles.
     const int lg = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = lg * 32 + lane;                       // row inside the current tile
@@ -244,81 +297,64 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         dlt = p.delta[li];
       }
       ok = bounded_wait(sdp_full, n & 1, abort_flag);
-      if (ok && n > 0) ok = bounded_wait(pds_free, (n - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (p.causal && it == jt) || (key0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+      uint4 packP[8], packD[8];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tmem_base + lane_base + cS + c * 32, rs);
         tmem_ld_32x32(tmem_base + lane_base + cDP + c * 32, rp);
         tc_wait_ld();
-        float pv[32], ds[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float pe = row_ok ? ex2_approx_b(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2)) : 0.f;
-          if (need_mask) {
-            const int64_t key = key0 + c * 32 + e;
-            if (key >= p.S || (p.causal && key > qrow)) pe = 0.f;
-          }
-          pv[e] = pe;
-          ds[e] = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
+        if (cc == 1) {                                  // S_i and dP_i are in registers: the MMA warp may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float pv[8], ds[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = q * 8 + e;
+            float pe = row_ok ? ex2_approx_b(fmaf(__uint_as_float(rs[col]), p.scale_log2, -lse2)) : 0.f;
+            if (need_mask) {
+              const int64_t key = key0 + c * 32 + col;
+              if (key >= p.S || (p.causal && key > qrow)) pe = 0.f;
+            }
+            pv[e] = pe;
+            ds[e] = pe * (__uint_as_float(rp[col]) - dlt) * p.scale;
+          }
+          __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&packP[cc * 4 + q]);
+          __nv_bfloat162* hd = reinterpret_cast<__nv_bfloat162*>(&packD[cc * 4 + q]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            ha[e] = __floats2bfloat162_rn(pv[2 * e], pv[2 * e + 1]);
+            hd[e] = __floats2bfloat162_rn(ds[2 * e], ds[2 * e + 1]);
+          }
+        }
+      }
+      if (n > 0) {                                      // the MMAs of tile n-1 have finished reading sP / sDS
+        ok = bounded_wait(pds_free, (n - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         const int cb = (c >> 1) * 16384;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 a, d;
-          __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
-          __nv_bfloat162* hd = reinterpret_cast<__nv_bfloat162*>(&d);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            ha[e] = __floats2bfloat162_rn(pv[q * 8 + 2 * e], pv[q * 8 + 2 * e + 1]);
-            hd[e] = __floats2bfloat162_rn(ds[q * 8 + 2 * e], ds[q * 8 + 2 * e + 1]);
-          }
           const int q16 = (((c & 1) * 4 + q) ^ sw) << 4;
-          *reinterpret_cast<uint4*>(prow + cb + q16) = a;
-          *reinterpret_cast<uint4*>(dsrow + cb + q16) = d;
+          *reinterpret_cast<uint4*>(prow + cb + q16) = packP[cc * 4 + q];
+          *reinterpret_cast<uint4*>(dsrow + cb + q16) = packD[cc * 4 + q];
         }
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_ready);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
-      // dQ_i partial: TMEM -> fp32 atomics
-      ok = bounded_wait(dq_full, n & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      // Each half-warp-group packs one [128 x 32] fp32 slab (128-byte swizzle) per round; one thread
-      // then hands both slabs to the TMA unit, which adds them into the fp32 accumulator in full
-      // 128-byte lines (scalar atomics from registers would be 8192 four-byte transactions per tile).
-      const bool issuer = (threadIdx.x == 64);
-#pragma unroll 1
-      for (int rd = 0; rd < DK / 64; ++rd) {
-        const int c = half * (DK / 64) + rd;
-        uint32_t raw[32];
-        tmem_ld_32x32(tmem_base + lane_base + cDQ + c * 32, raw);
-        tc_wait_ld();
-        if (issuer) bulk_wait_read0();            // the previous round's reduce has read its slabs
-        named_bar_sync(1, 256);
-        uint8_t* srow = sDQ + half * 16384 + r * 128;
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<uint4*>(srow + ((q ^ sw) << 4)) = make_uint4(raw[q * 4], raw[q * 4 + 1], raw[q * 4 + 2], raw[q * 4 + 3]);
-        fence_proxy_async_smem();
-        named_bar_sync(2, 256);
-        if (issuer) {
-          tma_reduce_add_4d(&tmDQ, sDQ, rd * 32, it * 128, h, b);
-          tma_reduce_add_4d(&tmDQ, sDQ + 16384, (DK / 64 + rd) * 32, it * 128, h, b);
-          bulk_commit();
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
     }
     // dV_j, dK_j: TMEM -> bf16 global (row = key)
     if (ok) {
@@ -356,7 +392,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (p.status) atomicExch(p.status, 0x23);
       *abort_flag = 1;
     }
-    if (threadIdx.x == 64) bulk_wait_all();       // reduce-adds must have left shared memory
   }
 
   tc_fence_before();
