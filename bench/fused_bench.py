@@ -110,7 +110,7 @@ def bench_rs_adam(rank, world, device, emit):
         link_ms = (world - 1) / world * n * 2 / (LINK_GBS * 1e9) * 1e3
         hbm_ms = hbm_bytes / (HBM_GBS * 1e9) * 1e3
         roof_ms = max(link_ms, hbm_ms)
-        emit({"bench": "rs_adam", "world": world, "bucket_mb": mb, "fused_ms": ms, "nccl_ms": ms_n,
+        emit({"bench": "rs_adam", "world": world, "bucket_mb": mb, "nvls": bool(dp.nvls), "fused_ms": ms, "nccl_ms": ms_n,
               "nvlink_bytes_per_gpu": link_bytes, "hbm_bytes_per_gpu": hbm_bytes, "nvlink_ms": link_ms, "hbm_ms": hbm_ms,
               "roofline_ms": roof_ms, "bound": "hbm" if hbm_ms > link_ms else "nvlink",
               "frac_of_roofline": roof_ms / ms})

@@ -31,6 +31,23 @@ __device__ __forceinline__ void st_peer_16(void* p, uint4 v) {
                : "memory");
 }
 
+// NVLS: the switch adds the 8 bf16 values at this offset of every rank's buffer (fp32 accumulation
+// inside the switch, result rounded to bf16) and returns the sums.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+// NVLS: one 16-byte store that the switch delivers to every rank's buffer.
+__device__ __forceinline__ void multimem_st_16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
 // Spin until *flag >= epoch. Returns false when the cycle budget runs out; never traps.
 __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long budget = kFlagWaitCycles) {
   if (ld_acquire_sys(flag) >= epoch) return true;

@@ -69,6 +69,10 @@ __device__ __forceinline__ void update_and_push(const dg_rs_optim_args& a, int64
   __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&outv);
 #pragma unroll
   for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(pw[2 * k], pw[2 * k + 1]);
+  if (a.param_mc) {   // NVLS: the switch writes the 16 bytes into every rank's buffer (this one included)
+    peer::multimem_st_16(reinterpret_cast<bf16*>(a.param_mc) + base + e0, outv);
+    return;
+  }
   for (int rr = 0; rr < W; ++rr) {
     const int r = (a.rank + rr) % W;  // start with the local copy, then rotate over peers
     bf16* dst = reinterpret_cast<bf16*>(a.param_ptrs[r]) + base + e0;
@@ -126,10 +130,36 @@ __global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
         update_and_push(a, e0, base, acc, load_state(a, e0), bc1, bc2);   // 3. + 4.
       }
     } else {
+      const int64_t tile = (int64_t)blockDim.x * U;
+      if (a.grad_mc) {
+        // NVLS pull: one in-switch reduction per 16 bytes
+        const bf16* mc = reinterpret_cast<const bf16*>(a.grad_mc) + base;
+        for (int64_t t0 = (int64_t)blockIdx.x * tile; t0 < nvec; t0 += (int64_t)gridDim.x * tile) {
+          OptState st[U];
+          uint4 raw[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
+            st[u] = load_state(a, (v < nvec ? v : 0) * 8);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
+            raw[u] = v < nvec ? peer::multimem_ld_reduce_bf16x8(mc + v * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int64_t v = t0 + (int64_t)u * blockDim.x + threadIdx.x;
+            if (v >= nvec) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            add_bf16x8(acc, raw[u]);
+            update_and_push(a, v * 8, base, acc, st[u], bc1, bc2);
+          }
+        }
+      } else {
       const bf16* srcs[WT];
 #pragma unroll
       for (int r = 0; r < WT; ++r) srcs[r] = reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base;
-      const int64_t tile = (int64_t)blockDim.x * U;
       for (int64_t t0 = (int64_t)blockIdx.x * tile; t0 < nvec; t0 += (int64_t)gridDim.x * tile) {
         // local optimizer state first, then the peer gradients: everything of this iteration is in
         // flight together (HBM and NVLink latencies overlap instead of adding up)
@@ -156,6 +186,7 @@ __global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
           for (int r = 0; r < WT; ++r) add_bf16x8(acc, raw[u][r]);   // fixed rank order: deterministic
           update_and_push(a, v * 8, base, acc, st[u], bc1, bc2);
         }
+      }
       }
     }
   }
@@ -197,6 +228,8 @@ extern "C" int dg_rs_optim(const dg_rs_optim_args* a, cudaStream_t stream) {
   if (a->shard_n <= 0 || a->shard_n % 8 != 0 || a->bucket_off % 8 != 0) return DG_ERR_BAD_ARG;
   if (!a->grad_ptrs || !a->param_ptrs || !a->flag_ptrs || !a->master || !a->counter) return DG_ERR_BAD_ARG;
   if (a->optimizer == 0 && (!a->m || !a->v || a->step < 1)) return DG_ERR_BAD_ARG;
+  if ((a->grad_mc == nullptr) != (a->param_mc == nullptr)) return DG_ERR_BAD_ARG;
+  if (a->grad_mc && a->world != 2 && a->world != 4 && a->world != 8) return DG_ERR_BAD_ARG;
   dg_rs_optim_args args = *a;
   if (args.wait_cycles <= 0) args.wait_cycles = dg::peer::kFlagWaitCycles;
   int64_t nvec = a->shard_n / 8;

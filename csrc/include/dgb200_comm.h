@@ -31,6 +31,11 @@ typedef struct {
   int* status;                    // device (or mapped host) int for error codes; may be null
   int max_ctas;                   // cap on the grid (0: default) so backward GEMMs keep their SMs
   long long wait_cycles;          // budget of each bounded wait (0: default, about two seconds)
+  // NVSwitch multicast addresses of the gradient and parameter buffers (NVLS), or null. When both are
+  // given the kernel reduces in the switch (one multimem.ld_reduce per 16 bytes instead of `world`
+  // peer loads; the sum comes back rounded to bf16) and pushes parameters with one multimem.st.
+  const void* grad_mc;
+  void* param_mc;
 } dg_rs_optim_args;
 int dg_rs_optim(const dg_rs_optim_args* args, cudaStream_t stream);
 

@@ -245,6 +245,8 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
       if (v < nvec) { xv[k].load(xr + v * VN); gv[k].load(gr + v * VN); }
     }
     const float mu = mean[row], rs = rstd[row];
+    // pass 1 over registers: xhat and g*gamma overwrite the cached x and g (packed back to the input
+    // type), so the second pass needs neither gamma nor the statistics again
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < KV; ++k) {
@@ -256,9 +258,11 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
           const float xh = (xf[e] - mu) * rs, gh = gf[e] * gm[e];
-          s1 += gh; s2 += gh * xh;
-          adg[k][e] += gf[e] * xh; adb[k][e] += gf[e];
+          s1 += gh; s2 = fmaf(gh, xh, s2);
+          adg[k][e] = fmaf(gf[e], xh, adg[k][e]); adb[k][e] += gf[e];
+          xf[e] = xh; gf[e] = gh;
         }
+        if (sizeof(T) == 4) { xv[k].pack(xf); gv[k].pack(gf); }   // fp32: exact; bf16 keeps x, g and recomputes below
       }
     }
     s1 = warp_sum(s1) / (float)d;
@@ -269,15 +273,21 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
       for (int k = 0; k < KV; ++k) {
         const int v = lane + 32 * k;
         if (v < nvec) {
-          float xf[VN], gf[VN], gm[VN], of[VN];
+          float xf[VN], gf[VN], of[VN];
           xv[k].unpack(xf); gv[k].unpack(gf);
-          Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
+          if (sizeof(T) == 4) {
 #pragma unroll
-          for (int e = 0; e < VN; ++e) {
-            const float xh = (xf[e] - mu) * rs;
-            of[e] = rs * (gf[e] * gm[e] - s1 - xh * s2);
+            for (int e = 0; e < VN; ++e) of[e] = rs * (gf[e] - s1 - xf[e] * s2);
+          } else {
+            float gm[VN];
+            Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+              const float xh = (xf[e] - mu) * rs;
+              of[e] = rs * (gf[e] * gm[e] - s1 - xh * s2);
+            }
           }
-          t.pack(of); t.store(o + v * VN);
+          Vec16<T> t2; t2.pack(of); t2.store(o + v * VN);
         }
       }
     }

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) reduce_cols_fused_kernel(T* __restrict__ 
                                                                 int64_t rows_per_split, int S, float scale,
                                                                 unsigned int counter_base) {
   constexpr int VN = Vec16<T>::N;
-  __shared__ float sh[8][32 * VN + 1];
+  __shared__ __align__(16) float sh[8][32 * VN + 1];   // also the 4 KB fold buffer (float4 access)
   __shared__ int s_last;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t b = blockIdx.z, s = blockIdx.y;
@@ -179,21 +179,41 @@ __global__ void __launch_bounds__(256) reduce_cols_fused_kernel(T* __restrict__ 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int i = threadIdx.x; i < 32 * VN; i += blockDim.x) {
-    const int64_t c = cb + i;
-    if (c < C) {
-      // four interleaved chains (k mod 4) keep four loads in flight; the grouping is fixed, so the
-      // sum is the same on every run
-      float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
-      const float* pp = partial + b * S * C + c;
-      int k = 0;
-      for (; k + 4 <= S; k += 4) {
-        t0 += __ldcg(pp + (int64_t)k * C); t1 += __ldcg(pp + (int64_t)(k + 1) * C);
-        t2 += __ldcg(pp + (int64_t)(k + 2) * C); t3 += __ldcg(pp + (int64_t)(k + 3) * C);
-      }
-      for (; k < S; ++k) t0 += __ldcg(pp + (int64_t)k * C);
-      stf(out, b * C + c, ((t0 + t1) + (t2 + t3)) * scale);
+  // Fold: G thread groups take the partials k = g, g + G, ... of four adjacent columns each (16-byte
+  // loads, two chains per thread), then the groups are added in group order: fixed grouping, so the
+  // sum is the same on every run.
+  constexpr int NC4 = 32 * VN / 4;          // float4 column groups of this CTA
+  constexpr int G = 256 / NC4;              // thread groups over the partials
+  float4* sfold = reinterpret_cast<float4*>(&sh[0][0]);   // G * NC4 float4 = 4 KB, inside sh
+  const int grp = threadIdx.x / NC4, c4 = threadIdx.x % NC4;
+  const int64_t c = cb + (int64_t)c4 * 4;
+  float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0;
+  if (c < C) {
+    const float* pp = partial + b * S * C + c;
+    int k = grp;
+    for (; k + G < S; k += 2 * G) {
+      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(pp + (int64_t)k * C));
+      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(pp + (int64_t)(k + G) * C));
+      t0.x += u0.x; t0.y += u0.y; t0.z += u0.z; t0.w += u0.w;
+      t1.x += u1.x; t1.y += u1.y; t1.z += u1.z; t1.w += u1.w;
     }
+    if (k < S) {
+      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(pp + (int64_t)k * C));
+      t0.x += u0.x; t0.y += u0.y; t0.z += u0.z; t0.w += u0.w;
+    }
+  }
+  __syncthreads();   // every thread is done with sh as the row-group buffer
+  sfold[grp * NC4 + c4] = make_float4(t0.x + t1.x, t0.y + t1.y, t0.z + t1.z, t0.w + t1.w);
+  __syncthreads();
+  if (grp == 0 && c < C) {
+    float4 r = sfold[c4];
+#pragma unroll
+    for (int g = 1; g < G; ++g) {
+      const float4 u = sfold[g * NC4 + c4];
+      r.x += u.x; r.y += u.y; r.z += u.z; r.w += u.w;
+    }
+    stf(out, b * C + c, r.x * scale); stf(out, b * C + c + 1, r.y * scale);
+    stf(out, b * C + c + 2, r.z * scale); stf(out, b * C + c + 3, r.w * scale);
   }
 }
 
@@ -265,7 +285,7 @@ __global__ void __launch_bounds__(256) sum_all_fold_kernel(T* __restrict__ out, 
 static inline int cols_splits(int64_t B, int64_t R, int64_t C) {
   int64_t col_blocks = (C + 255) / 256;
   int64_t want = (148 * 2 + B * col_blocks - 1) / (B * col_blocks);
-  int64_t max_s = (R + 63) / 64;
+  int64_t max_s = (R + 255) / 256;   // at least 256 rows per split: the fold costs one round trip per few splits
   if (want > max_s) want = max_s;
   if (want < 1) want = 1;
   if (want > 256) want = 256;

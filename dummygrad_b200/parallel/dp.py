@@ -22,6 +22,7 @@ forward waits (on the device) for the "landed" flags of every bucket from every 
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from dataclasses import dataclass, field
 
@@ -44,7 +45,7 @@ class RsOptimArgs(C.Structure):
         ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float), ("wd", C.c_float),
         ("grad_scale", C.c_float),
         ("optimizer", C.c_int), ("counter", C.c_void_p), ("status", C.c_void_p), ("max_ctas", C.c_int),
-        ("wait_cycles", C.c_longlong),
+        ("wait_cycles", C.c_longlong), ("grad_mc", C.c_void_p), ("param_mc", C.c_void_p),
     ]
 
 
@@ -144,6 +145,7 @@ class DataParallel:
         self.epoch = 0
         self.accum_steps = 1
         self._sync = True
+        self.nvls = False
 
         # ---- flat layout, buckets in reverse parameter order
         order = list(reversed(range(len(params))))
@@ -196,6 +198,10 @@ class DataParallel:
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.comm_stream = torch.cuda.Stream(self.device)
             self.lib = _bind_comm(L.load())
+            # In-switch reduction (NVLS multimem) when the fabric offers multicast for both buffers and
+            # DG_NVLS=1 asks for it; gradients are then summed in the switch and come back as bf16.
+            self.nvls = (os.environ.get("DG_NVLS", "0") == "1" and self.world in (2, 4, 8)
+                         and self.grad_buf.multicast_ptr != 0 and self.param_buf.multicast_ptr != 0)
         if dist.is_initialized():
             dist.barrier(group)
 
@@ -252,6 +258,8 @@ class DataParallel:
         a.status = self.status.data_ptr()
         a.max_ctas = self.max_comm_ctas
         a.wait_cycles = self.wait_cycles
+        if self.nvls:
+            a.grad_mc, a.param_mc = self.grad_buf.multicast_ptr, self.param_buf.multicast_ptr
         L.check(self.lib.dg_rs_optim(C.byref(a), self.comm_stream.cuda_stream), "dg_rs_optim")
         K._cnt()
 

@@ -43,6 +43,8 @@ class SymmBuffer:
         """NVLS multicast address of the buffer (0 when the fabric or the driver has none)."""
         if self.handle is None or not getattr(self.handle, "has_multicast_support", lambda: False)():
             return 0
+        if self.ptrs[self.rank] != self.tensor.data_ptr():
+            return 0        # the tensor does not start at the allocation base: offsets would not line up
         return int(self.handle.multicast_ptr)
 
     def peer_tensor(self, rank: int, shape, dtype=None) -> torch.Tensor:

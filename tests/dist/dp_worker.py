@@ -75,6 +75,18 @@ def main():
         ls, ws, _ = run("fused", 0, 1, device, ids, tgt, 4, solo=True)
         err = max(abs(a - b) for a, b in zip(lf, ls))
         assert err < 3e-2, f"{world}-GPU vs 1-GPU loss: {lf} vs {ls}"
+    # NVLS variant of the same kernel (in-switch reduction + multicast store), where the fabric has it
+    os.environ["DG_NVLS"] = "1"
+    ln, wn, tr_n = run("fused", rank, world, device, ids, tgt, 4)
+    os.environ["DG_NVLS"] = "0"
+    if tr_n.dp.nvls:
+        err_n = max(abs(a - b) for a, b in zip(ln, lc))
+        mean_n = (wn - wc).abs().mean().item()
+        assert err_n < 2e-2 and mean_n < 2e-3, f"NVLS vs NCCL: loss {err_n}, weights mean {mean_n}"
+        refn = wn.clone()
+        dist.broadcast(refn, 0)
+        assert (wn - refn).abs().max().item() == 0.0, "ranks diverged after the multicast parameter push"
+    nvls_note = "nvls=checked" if tr_n.dp.nvls else "nvls=unavailable"
     # bounded wait: wait on flags nobody sets -> status code, no hang
     import ctypes as C
     from dummygrad_b200 import _lib as L
@@ -87,7 +99,7 @@ def main():
     assert int(status.item()) != 0, "an unsatisfied wait must report a status"
     dist.barrier()
     if rank == 0:
-        print(f"DP_WORKER_OK world={world} fused={lf} nccl={lc}")
+        print(f"DP_WORKER_OK world={world} {nvls_note} fused={lf} nccl={lc}")
     D.shutdown()
 
 
