@@ -41,11 +41,14 @@ class SymmBuffer:
     @property
     def multicast_ptr(self) -> int:
         """NVLS multicast address of the buffer (0 when the fabric or the driver has none)."""
-        if self.handle is None or not getattr(self.handle, "has_multicast_support", lambda: False)():
+        if self.handle is None:
             return 0
         if self.ptrs[self.rank] != self.tensor.data_ptr():
             return 0        # the tensor does not start at the allocation base: offsets would not line up
-        return int(self.handle.multicast_ptr)
+        try:
+            return int(self.handle.multicast_ptr or 0)
+        except (AttributeError, RuntimeError):
+            return 0
 
     def peer_tensor(self, rank: int, shape, dtype=None) -> torch.Tensor:
         """A view of ``rank``'s buffer (for tests and NCCL-free debugging; not used on hot paths)."""
