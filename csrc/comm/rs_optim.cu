@@ -17,6 +17,7 @@
 // The reference has no counterpart: its optimizer is a host loop over one tensor
 // (src/optimizers.h:32-59); the update rule here is the same.
 #include "../kernels/common.cuh"
+#include "../kernels/sm100_ptx.cuh"
 #include "peer.cuh"
 #include "../include/dgb200_comm.h"
 
@@ -206,6 +207,159 @@ __global__ void __launch_bounds__(256) rs_optim_kernel(dg_rs_optim_args a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Bulk-copy variant of the same step for large shards. One producer thread per CTA streams tiles of
+// kRsTile elements - the fp32 master / moment slices from this GPU and the bf16 gradient slice of
+// EVERY rank (peer memory included; plain bulk copies, no multicast) - into a ring of shared-memory
+// stages; eight consumer warps take a stage when its mbarrier completes, sum the gradients in rank
+// order, update, and store straight to global / peer memory. The copy engine keeps several stages of
+// HBM and NVLink reads in flight per SM without spending registers on them.
+constexpr int kRsTile = 2048;        // elements per stage
+constexpr int kRsStages = 3;
+constexpr int kRsThreads = 288;      // 8 consumer warps + 1 producer warp
+constexpr int kRsStateBytes = 3 * kRsTile * 4;
+
+using sm100::bounded_wait;
+using sm100::mbar_arrive;
+using sm100::mbar_expect_tx;
+using sm100::mbar_init;
+
+__device__ __forceinline__ void rs_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   sm100::smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(sm100::smem_u32(bar))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kRsThreads, 1) rs_optim_ring_kernel(dg_rs_optim_args a) {
+  extern __shared__ uint8_t rs_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(rs_smem_raw) + 127) & ~uintptr_t(127));
+  __shared__ uint64_t bars[2 * kRsStages];
+  __shared__ int s_ok;
+  __shared__ volatile int s_abort;
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kRsStages;
+  const int W = a.world;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* my_pad = a.flag_ptrs[a.rank];
+  const int ready_base = a.bucket_id * W;
+  const int done_base = a.n_buckets * W + a.bucket_id * W;
+  const uint32_t stage_bytes = kRsStateBytes + (uint32_t)W * kRsTile * 2;
+
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < W; ++r) peer::st_release_sys(a.flag_ptrs[r] + ready_base + a.rank, a.epoch);
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRsStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
+    sm100::fence_barrier_init();
+    s_abort = 0;
+    int ok = 1;
+    for (int r = 0; r < W && ok; ++r) ok = peer::wait_flag(my_pad + ready_base + r, a.epoch, a.wait_cycles) ? 1 : 0;
+    if (!ok && a.status) atomicExch(a.status, 0x100 | a.bucket_id);
+    s_ok = ok;
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+
+  if (ok) {
+    const int64_t n = a.shard_n;
+    const int64_t tiles = (n + kRsTile - 1) / kRsTile;
+    const int64_t base = a.bucket_off + (int64_t)a.rank * a.shard_n;
+    const bool adam = a.optimizer == 0;
+    if (warp == 8) {
+      // ------------------------------------------------------------------ producer
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t last_parity[kRsStages];
+        bool used[kRsStages];
+        for (int s = 0; s < kRsStages; ++s) { last_parity[s] = 0; used[s] = false; }
+        bool pok = true;
+        for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+          pok = bounded_wait(&empty[stage], phase ^ 1u, &s_abort, a.wait_cycles);
+          if (!pok) break;
+          const int64_t e0 = t * kRsTile;
+          const uint32_t cnt = (uint32_t)((n - e0) < kRsTile ? (n - e0) : kRsTile);
+          mbar_expect_tx(&full[stage], cnt * 4u * (adam ? 3u : 1u) + (uint32_t)W * cnt * 2u);
+          uint8_t* sp = smem + stage * stage_bytes;
+          rs_bulk_load(sp, a.master + e0, cnt * 4u, &full[stage]);
+          if (adam) {
+            rs_bulk_load(sp + kRsTile * 4, a.m + e0, cnt * 4u, &full[stage]);
+            rs_bulk_load(sp + 2 * kRsTile * 4, a.v + e0, cnt * 4u, &full[stage]);
+          }
+          for (int r = 0; r < W; ++r)
+            rs_bulk_load(sp + kRsStateBytes + r * (kRsTile * 2), reinterpret_cast<const bf16*>(a.grad_ptrs[r]) + base + e0,
+                         cnt * 2u, &full[stage]);
+          used[stage] = true;
+          last_parity[stage] = phase;
+          if (++stage == kRsStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!pok) {
+          if (a.status && !s_abort) atomicExch(a.status, 0x110 | a.bucket_id);
+          s_abort = 1;
+        }
+        if (s_abort) {
+          // someone gave up: nothing of this CTA may still be in flight towards its shared memory
+          volatile int never = 0;
+          for (int s = 0; s < kRsStages; ++s)
+            if (used[s]) bounded_wait(&full[s], last_parity[s], &never, a.wait_cycles);
+        }
+      }
+    } else {
+      // ------------------------------------------------------------------ consumers (warps 0..7)
+      const float bc1 = 1.f - powf(a.beta1, (float)a.step), bc2 = 1.f - powf(a.beta2, (float)a.step);
+      int stage = 0;
+      uint32_t phase = 0;
+      const int v = threadIdx.x;           // one 8-element vector per thread and tile
+      for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        bool w = bounded_wait(&full[stage], phase, &s_abort, a.wait_cycles);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) {
+          if (lane == 0) { if (a.status && !s_abort) atomicExch(a.status, 0x120 | a.bucket_id); s_abort = 1; }
+          break;
+        }
+        const int64_t e0 = t * kRsTile;
+        const int64_t cnt = (n - e0) < kRsTile ? (n - e0) : kRsTile;
+        const uint8_t* sp = smem + stage * stage_bytes;
+        if ((int64_t)v * 8 < cnt) {
+          OptState st;
+          const float4* pm = reinterpret_cast<const float4*>(sp) + v * 2;
+          st.p0 = pm[0]; st.p1 = pm[1];
+          if (adam) {
+            const float4* mm = reinterpret_cast<const float4*>(sp + kRsTile * 4) + v * 2;
+            const float4* vv = reinterpret_cast<const float4*>(sp + 2 * kRsTile * 4) + v * 2;
+            st.m0 = mm[0]; st.m1 = mm[1]; st.v0 = vv[0]; st.v1 = vv[1];
+          } else {
+            st.m0 = st.m1 = st.v0 = st.v1 = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < W; ++r)     // rank order: deterministic
+            add_bf16x8(acc, *reinterpret_cast<const uint4*>(sp + kRsStateBytes + r * (kRsTile * 2) + v * 16));
+          update_and_push(a, e0 + (int64_t)v * 8, base, acc, st, bc1, bc2);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);   // this warp has read everything it needs from the stage
+        if (++stage == kRsStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  }
+
+  // last CTA publishes completion (not after a failure: the peers' bounded waits report it)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(a.counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *a.counter = 0;
+      __threadfence_system();
+      if (ok && !s_abort) {
+        for (int r = 0; r < W; ++r) peer::st_release_sys(a.flag_ptrs[r] + done_base + a.rank, a.epoch);
+      }
+    }
+  }
+}
+
 __global__ void flags_wait_kernel(const int* flags, int n, int epoch, int* status, long long wait_cycles) {
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     if (!peer::wait_flag(flags + i, epoch, wait_cycles)) {
@@ -233,6 +387,25 @@ extern "C" int dg_rs_optim(const dg_rs_optim_args* a, cudaStream_t stream) {
   dg_rs_optim_args args = *a;
   if (args.wait_cycles <= 0) args.wait_cycles = dg::peer::kFlagWaitCycles;
   int64_t nvec = a->shard_n / 8;
+  // large shards: bulk-copy ring (not with NVLS, where the switch already does the reduction)
+  static int ring_mode = -1;          // DG_RS_RING=0 keeps the register kernel for every size
+  if (ring_mode < 0) { const char* e = getenv("DG_RS_RING"); ring_mode = (e && e[0] == '0') ? 0 : 1; }
+  if (ring_mode && !a->grad_mc && a->world <= 8 && a->shard_n >= 16 * dg::kRsTile) {
+    const int64_t tiles = (a->shard_n + dg::kRsTile - 1) / dg::kRsTile;
+    int cap = a->max_ctas > 0 ? a->max_ctas : 148;
+    if (cap > 148) cap = 148;
+    const int blocks = (int)(tiles < cap ? tiles : cap);
+    const size_t smem = (size_t)dg::kRsStages * (dg::kRsStateBytes + (size_t)a->world * dg::kRsTile * 2) + 128;
+    static size_t attr_smem = 0;
+    if (smem > attr_smem) {
+      cudaError_t e = cudaFuncSetAttribute(dg::rs_optim_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      attr_smem = smem;
+    }
+    dg::rs_optim_ring_kernel<<<blocks, dg::kRsThreads, smem, stream>>>(args);
+    DG_CHECK_LAUNCH();
+    return DG_OK;
+  }
   const int U = a->world >= 4 ? 2 : 4;
   int64_t want = (nvec + 256 * U - 1) / (256 * U);
   int cap = a->max_ctas > 0 ? a->max_ctas : 148 * 2;
