@@ -1,0 +1,107 @@
+"""GPU numerics of the one-launch kernels against plain fp32 PyTorch: column sums with the last-CTA
+fold, split-K fold, fused LayerNorm backward (all register-tiling variants), with bitwise
+run-to-run determinism."""
+import pytest
+import torch
+
+from dummygrad_b200 import _lib as L
+from dummygrad_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("shape,dtype", [((1, 5000, 1000), torch.bfloat16), ((1, 70000, 4096), torch.bfloat16),
+                                          ((3, 700, 256), torch.float32), ((1, 8192, 1024), torch.bfloat16),
+                                          ((2, 33, 24), torch.float32), ((1, 300, 1001), torch.float32)])
+def test_reduce_cols_sum_and_mean(shape, dtype):
+    torch.manual_seed(0)
+    x = torch.randn(shape, device=DEV).to(dtype)
+    for mode, ref in ((L.RED_SUM, x.float().sum(1)), (L.RED_MEAN, x.float().mean(1))):
+        out, _ = K.reduce_cols(x, mode)
+        out2, _ = K.reduce_cols(x, mode)
+        assert torch.equal(out, out2), "column reduction must be deterministic"
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+        scale = ref.abs().max().item() + 1.0
+        assert (out.float() - ref).abs().max().item() <= tol * scale
+
+
+def test_reduce_cols_into_given_buffer():
+    x = torch.randn(1, 4096, 512, device=DEV).to(torch.bfloat16)
+    buf = torch.zeros(1, 512, dtype=torch.bfloat16, device=DEV)
+    out, _ = K.reduce_cols(x, L.RED_SUM, out=buf)
+    assert out.data_ptr() == buf.data_ptr()
+    assert (buf.float() - x.float().sum(1)).abs().max().item() < 0.5
+
+
+@pytest.mark.parametrize("M,N,Kd", [(256, 384, 16384), (1024, 1024, 8192), (128, 4096, 65536)])
+def test_split_k_fold_into_given_buffer(M, N, Kd):
+    torch.manual_seed(1)
+    a = (torch.randn(Kd, M, device=DEV) * 0.1).to(torch.bfloat16)
+    b = (torch.randn(Kd, N, device=DEV) * 0.1).to(torch.bfloat16)
+    sink = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    out = K.gemm2d(a, b, trans_a=True, out=sink)
+    assert out.data_ptr() == sink.data_ptr()
+    ref = a.float().t() @ b.float()
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * (ref.abs().max().item() + 1.0)
+    assert torch.equal(K.gemm2d(a, b, trans_a=True), out)
+
+
+@pytest.mark.parametrize("rows,d,dtype", [(8192, 1024, torch.bfloat16), (4096, 2048, torch.bfloat16),
+                                          (300, 64, torch.bfloat16), (1000, 512, torch.bfloat16),
+                                          (777, 1024, torch.float32), (64, 256, torch.float32), (5, 72, torch.float32)])
+def test_layernorm_backward_fused(rows, d, dtype):
+    torch.manual_seed(2)
+    x = torch.randn(rows, d, device=DEV).to(dtype)
+    g = torch.randn(rows, d, device=DEV).to(dtype)
+    gamma = (1.0 + 0.1 * torch.randn(d, device=DEV)).to(dtype)
+    beta = torch.zeros(d, device=DEV, dtype=dtype)
+    y, mu, rs = K.layernorm_fwd(x, gamma, beta, 1e-5)
+    dx, dg_, db = K.layernorm_bwd(g, x, gamma, mu, rs)
+    dx2, dg2, db2 = K.layernorm_bwd(g, x, gamma, mu, rs)
+    assert torch.equal(dx, dx2) and torch.equal(dg_, dg2) and torch.equal(db, db2)
+    xt = x.float().requires_grad_(True)
+    gt = gamma.float().requires_grad_(True)
+    bt = beta.float().requires_grad_(True)
+    torch.nn.functional.layer_norm(xt, (d,), gt, bt, 1e-5).backward(g.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    for got, ref, what in ((dx, xt.grad, "dx"), (dg_, gt.grad, "dgamma"), (db, bt.grad, "dbeta")):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= tol * (ref.abs().max().item() + 1.0), f"{what}: {err}"
+
+
+def test_parameter_gradients_land_in_their_sinks():
+    """Linear / LayerNorm backward write dW, db, dgamma, dbeta straight into a registered sink."""
+    import dummygrad_b200 as dg
+    from dummygrad_b200.ops import functional as F
+    dg.set_default_device(DEV)
+    dg.manual_seed(0)
+    x = dg.Tensor.from_torch((torch.randn(256, 128, device=DEV) * 0.5).to(torch.bfloat16), True)
+    lin = dg.models.layers.Linear(128, 256, dtype=torch.bfloat16, device=torch.device(DEV))
+    ln = dg.models.layers.LayerNorm(256, dtype=torch.bfloat16, device=torch.device(DEV))
+    params = lin.parameters() + ln.parameters()
+    sinks = [torch.full_like(p.data, 7.0) for p in params]
+    for p, s in zip(params, sinks):
+        p.set_grad_sink(s)
+    before = K.launch_count
+    loss = dg.simple_sum(ln.forward(lin.forward(x)))
+    loss.backward()
+    for p, s in zip(params, sinks):
+        assert p.grad is not None and p.grad.data.data_ptr() == s.data_ptr()
+    # same values as without sinks
+    for p in params:
+        p.set_grad_sink(None)
+    x2 = dg.Tensor.from_torch(x.data.clone(), True)
+    dg.simple_sum(ln.forward(lin.forward(x2))).backward()
+    for p, s in zip(params, sinks):
+        assert torch.equal(p.grad.data, s)
+    # second backward into filled sinks accumulates (gradient accumulation across micro-batches)
+    for p, s in zip(params, sinks):
+        p.set_grad_sink(s.clone())
+        p._sink_filled = True
+    x3 = dg.Tensor.from_torch(x.data.clone(), True)
+    dg.simple_sum(ln.forward(lin.forward(x3))).backward()
+    for p, s in zip(params, sinks):
+        ref = (s.float() * 2)
+        assert (p.grad.data.float() - ref).abs().max().item() <= 2e-2 * (ref.abs().max().item() + 1.0)
+    assert before < K.launch_count
