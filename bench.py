@@ -333,7 +333,7 @@ def run_reference(args) -> dict:
     if args.config in ("gpt350m", "gpt1p3b"):
         return {"impl": "reference",
                 "unavailable": "reference is a single-threaded fp32 CPU header library with no GPU or distributed path: "
-                               "one step of this config is >1e17 FLOP at ~1 GFLOP/s (years); run --config toy or mlp"}
+                               "one step of this config is about 1.5e14 FLOP at about 1 GFLOP/s (more than a day per step); run --config toy or mlp"}
     harness = "ref_toy.cpp" if args.config == "toy" else "ref_mlp.cpp"
     exe = os.path.join(ROOT, "build", harness.replace(".cpp", ""))
     os.makedirs(os.path.dirname(exe), exist_ok=True)
