@@ -155,9 +155,17 @@ class MultiHeadAttention(Module):
             x = F.reshape(x, [1, x.shape[0], x.shape[1]])
         B, S = x.shape[0], x.shape[1]
         H, dk = self.n_heads, self.d_k
-        q, k, v = self.W_q.forward(x), self.W_k.forward(x), self.W_v.forward(x)
         scale = 1.0 / math.sqrt(dk)
-        if self.fused:
+        merged = None
+        if self.fused and self.W_q.b is not None:
+            # projections + attention as one node (their three input gradients are summed in GEMM epilogues)
+            merged = F.attention_block(x, self.W_q.W, self.W_q.b, self.W_k.W, self.W_k.b, self.W_v.W, self.W_v.b, H,
+                                       causal=self.causal, scale=scale)
+        if merged is None:
+            q, k, v = self.W_q.forward(x), self.W_k.forward(x), self.W_v.forward(x)
+        if merged is not None:
+            pass
+        elif self.fused:
             merged = F.mha_core(q, k, v, H, causal=self.causal, scale=scale)
         else:
             qs = F.transpose(F.reshape(q, [B, S, H, dk]), 1, 2)

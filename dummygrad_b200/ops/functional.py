@@ -1212,6 +1212,66 @@ def mha_core(q: Tensor, k: Tensor, v: Tensor, n_heads: int, causal: bool = False
     return _result(od, lambda: MhaCoreBackward(AttentionBackward(qd, kd, vd, p, scale, causal), B, S, H, dk), (q, k, v))
 
 
+class AttentionBlockBackward(Node):
+    """Backward of attention(x Wq + bq, x Wk + bk, x Wv + bv): the three input gradients are summed in
+    the GEMM epilogues (dx = dq Wq^T, then += dk Wk^T, += dv Wv^T through the residual input) instead
+    of three separate [tokens, d] tensors and two add kernels."""
+
+    def __init__(self, x2d, Ws, q, k, v, o, lse, H, causal, scale, xshape, leaves):
+        super().__init__()
+        self.x2d, self.Ws, self.saved = x2d, Ws, (q, k, v, o, lse)
+        self.H, self.causal, self.scale, self.xshape, self.leaves = H, causal, scale, xshape, leaves
+
+    def apply(self, grads):
+        q, k, v, o, lse = self.saved
+        x2d = self.x2d
+        T_, d = x2d.shape
+        g = _grad(grads, q.shape, q.dtype, q.device)
+        dqkv = K.attention_bwd(q, k, v, o, g, lse, self.H, self.causal, self.scale)
+        dt = g.dtype
+        outs = [None]
+        dx = None
+        for i, (dy, W) in enumerate(zip(dqkv, self.Ws)):
+            dy2 = dy.reshape(T_, -1)
+            n_out = dy2.shape[1]
+            tW, tb = self.leaves[2 * i], self.leaves[2 * i + 1]
+            dW = K.gemm2d(x2d, dy2, trans_a=True, out=_sink(tW, dt, d * n_out))
+            db, _ = K.reduce_cols(dy2.reshape(1, T_, n_out), RED_SUM, out=_sink(tb, dt, n_out))
+            dx = K.gemm2d(dy2, W, trans_b=True) if dx is None else K.gemm2d(dy2, W, trans_b=True, residual=dx, out=dx)
+            outs += [dW, db.reshape(1, n_out)]
+        outs[0] = dx.reshape(self.xshape)
+        return outs
+
+    def release_variables(self):
+        self.x2d = self.Ws = self.saved = None
+
+
+def attention_block(x: Tensor, Wq: Tensor, bq: Tensor, Wk: Tensor, bk: Tensor, Wv: Tensor, bv: Tensor, n_heads: int,
+                    causal: bool = False, scale: float | None = None) -> Tensor | None:
+    """q/k/v projections + multi-head attention of x [B, S, d] as ONE autograd node (the part of
+    src/attention.h:72-93 before the output projection). Returns None when the fused attention
+    kernel does not support the shape (the caller then uses the op-by-op path)."""
+    if x.ndim() != 3:
+        return None
+    B, S, d = x.shape
+    D = Wq.shape[1]
+    if Wk.shape[1] != D or Wv.shape[1] != D or D % n_heads:
+        return None
+    dk = D // n_heads
+    scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    xd = _c(x).reshape(B * S, d)
+    if not (xd.is_cuda and x.dtype == torch.bfloat16 and Wq.dtype == x.dtype and dk in (64, 128)):
+        return None
+    Ws = [_c(Wq), _c(Wk), _c(Wv)]
+    qkv = [K.gemm2d(xd, W, bias=_c(b).reshape(D)).reshape(B, S, D) for W, b in zip(Ws, (bq, bk, bv))]
+    if not K.attention_supported(qkv[0], n_heads):
+        return None
+    od, lse = K.attention_fwd(qkv[0], qkv[1], qkv[2], n_heads, causal, scale)
+    return _result(od, lambda: AttentionBlockBackward(xd, Ws, qkv[0], qkv[1], qkv[2], od, lse, n_heads, causal, scale,
+                                                      tuple(x.shape), (Wq, bq, Wk, bk, Wv, bv)),
+                   (x, Wq, bq, Wk, bk, Wv, bv))
+
+
 class MlpBackward(Node):
     """Backward of fc2(gelu(fc1(x))) (+ residual). The GELU derivative runs in the epilogue of the
     GEMM that produces dH, so the [tokens, d_ff] gradient is written once."""

@@ -105,3 +105,39 @@ def test_parameter_gradients_land_in_their_sinks():
         ref = (s.float() * 2)
         assert (p.grad.data.float() - ref).abs().max().item() <= 2e-2 * (ref.abs().max().item() + 1.0)
     assert before < K.launch_count
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_block_matches_op_chain(causal):
+    """Fused projections + attention node (input gradients summed in GEMM epilogues) against the
+    op-by-op MultiHeadAttention on the same bf16 weights."""
+    import dummygrad_b200 as dg
+    dev = torch.device(DEV)
+    dg.set_default_device(dev)
+    dg.manual_seed(3)
+    fused = dg.MultiHeadAttention(128, 2, causal, dtype=torch.bfloat16, device=dev, fused=True)
+    plain = dg.MultiHeadAttention(128, 2, causal, dtype=torch.bfloat16, device=dev, fused=False)
+    for a, b in zip(plain.parameters(), fused.parameters()):
+        a.data.copy_(b.data)
+    torch.manual_seed(4)
+    xv = (torch.randn(2, 256, 128, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2, 256, 128, device=DEV)).to(torch.bfloat16)
+    outs = []
+    for m in (fused, plain):
+        x = dg.Tensor.from_torch(xv.clone(), True)
+        y = m.forward(x)
+        dg.simple_sum(dg.mul(y, dg.Tensor.from_torch(w, False))).backward()
+        outs.append((y.data.float(), x.grad.data.float(), [p.grad.data.float().clone() for p in m.parameters()]))
+    (yf, gxf, gpf), (yp, gxp, gpp) = outs
+
+    def rel(a, b):
+        return (a - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+
+    assert rel(yf, yp) < 3e-2, rel(yf, yp)
+    assert rel(gxf, gxp) < 4e-2, rel(gxf, gxp)
+    # the key-bias gradient is zero in exact arithmetic (softmax rows of dS sum to zero), so it is pure
+    # rounding noise on both sides: bound every gradient against the largest gradient scale as well
+    gmax = max(b.abs().max().item() for b in gpp)
+    for a, b in zip(gpf, gpp):
+        err = (a.reshape(-1) - b.reshape(-1)).abs().max().item()
+        assert err <= 4e-2 * max(b.abs().max().item(), 0.05 * gmax), (err, b.abs().max().item(), gmax)
