@@ -140,7 +140,18 @@ __global__ void __launch_bounds__(256) reduce_cols_fused_kernel(T* __restrict__ 
   if (c0 < C) {
     const T* p = x + b * R * C + c0;
     int64_t r = r0 + ty;
-    for (; r + 8 < r1; r += 16) {   // two independent 16-byte loads in flight per thread
+    for (; r + 56 < r1; r += 64) {  // eight independent 16-byte loads in flight per thread
+      Vec16<T> t[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t[i].load(p + (r + 8 * i) * C);
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        float f0[VN], f1[VN]; t[i].unpack(f0); t[i + 1].unpack(f1);
+#pragma unroll
+        for (int k = 0; k < VN; ++k) acc[k] += f0[k] + f1[k];
+      }
+    }
+    for (; r + 8 < r1; r += 16) {   // two at a time
       Vec16<T> t0, t1; t0.load(p + r * C); t1.load(p + (r + 8) * C);
       float f0[VN], f1[VN]; t0.unpack(f0); t1.unpack(f1);
 #pragma unroll
