@@ -176,7 +176,20 @@ extern "C" int dg_gemm_sm100_supported(const dg_gemm_args* a) {
 extern "C" int dg_gemm_sm100(const dg_gemm_args* a, cudaStream_t stream) {
   using namespace dg::sm100;
   if (!dg_gemm_sm100_supported(a)) return DG_ERR_UNSUPPORTED;
-  const int BN = a->N > 128 ? 256 : 128;
+  int BN = a->N > 128 ? 256 : 128;
+  {
+    // Tile-width choice. 128 x 256 tiles read fewer operand bytes per FLOP (the better choice when
+    // there are many tiles per SM); 128 x 128 tiles give twice as many tiles, which fills the SMs and
+    // shortens the un-overlapped first load / last epilogue when there are only a few tiles per SM.
+    // DG_GEMM_BN=128|256 overrides the heuristic (tuning experiments).
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("DG_GEMM_BN"); forced = e ? atoi(e) : 0; }
+    static int small_limit = -1;
+    if (small_limit < 0) { const char* e = getenv("DG_GEMM_SMALL_TILES"); small_limit = e ? atoi(e) : 0; }
+    const int64_t tiles256 = ((a->M + 127) / 128) * ((a->N + 255) / 256) * a->batch;
+    if (forced == 128 || forced == 256) BN = a->N > 128 ? forced : 128;
+    else if (BN == 256 && small_limit > 0 && tiles256 < (int64_t)small_limit * sm_count()) BN = 128;
+  }
   CUtensorMap tmA, tmB;
   int rc = build_operand_maps(&tmA, &tmB, a, BN);
   if (rc) return rc;

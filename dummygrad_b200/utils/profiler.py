@@ -19,10 +19,11 @@ from .. import _lib as L
 
 
 class _Proxy:
-    def __init__(self, lib, records):
+    def __init__(self, lib, records, nvtx: bool = False):
         object.__setattr__(self, "_lib", lib)
         object.__setattr__(self, "_records", records)
         object.__setattr__(self, "_cache", {})
+        object.__setattr__(self, "_nvtx", nvtx)
 
     def __getattr__(self, name):
         fn = getattr(self._lib, name)
@@ -33,6 +34,7 @@ class _Proxy:
         if cached is not None:
             return cached
         records = self._records
+        nvtx = self._nvtx
 
         def wrapped(*args):
             key = name
@@ -42,6 +44,12 @@ class _Proxy:
                 g = args[0]._obj
                 lay = ("n" if g.a_kmajor else "t") + ("t" if g.b_kmajor else "n")
                 key = f"dg_gemm_sm100[{lay} {g.M}x{g.N}x{g.K}" + (f" b{g.batch}]" if g.batch > 1 else "]")
+            if nvtx:     # a named range per launch for timeline tools; no events, no timing table
+                torch.cuda.nvtx.range_push(key)
+                try:
+                    return fn(*args)
+                finally:
+                    torch.cuda.nvtx.range_pop()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             rc = fn(*args)
@@ -83,11 +91,13 @@ class Profile:
 
 
 @contextlib.contextmanager
-def profile():
-    """Profile every kernel-library launch made inside the block (CUDA only)."""
+def profile(nvtx: bool = False):
+    """Profile every kernel-library launch made inside the block (CUDA only). With ``nvtx=True`` each
+    launch is wrapped in an NVTX range named like the table rows (kernel, layout, shape) instead of
+    being timed, so that timelines of external tools are readable."""
     lib = L.load()
     prof = Profile()
-    proxy = _Proxy(lib, prof.records)
+    proxy = _Proxy(lib, prof.records, nvtx)
     saved = L._LIB
     L._LIB = proxy
     try:
