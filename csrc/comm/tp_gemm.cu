@@ -324,6 +324,8 @@ extern "C" int dg_gemm_rs(const dg_gemm_rs_args* a, cudaStream_t stream) {
   p.own_staging = a->staging; p.own_flags = a->tile_flags; p.stage_ld = a->N; p.world = a->world;
   p.dest_base = a->dest_slots; p.rows_per_dest = rows_per_rank; p.dest_flags = a->tile_flag_ptrs;
   p.src_rank = a->rank; p.d_epoch = a->epoch;
+  p.addend = a->addend; p.addend_ld = a->ld_addend;
+  if (a->addend && (a->ld_addend < a->N || a->ld_addend % 8)) return DG_ERR_BAD_ARG;
   // start with the tiles owned by the next rank so that all links carry data from the beginning
   p.m_tile_rotate = (int64_t)((a->rank + 1) % a->world) * rows_per_rank / 128;
   RsRole r;

@@ -113,6 +113,10 @@ int64_t dg_layernorm_bwd_scratch_bytes(int64_t rows, int64_t d);
 int dg_layernorm_bwd(int dtype, void* dx, void* dgamma, void* dbeta, const void* g, const void* x,
                      const void* gamma, const float* mean, const float* rstd, int64_t rows,
                      int64_t d, void* scratch, cudaStream_t stream);
+// dg_layernorm_bwd with dx = input gradient + dx_addend (fused kernel only; DG_ERR_UNSUPPORTED otherwise).
+int dg_layernorm_bwd_add(int dtype, void* dx, void* dgamma, void* dbeta, const void* g, const void* x, const void* gamma,
+                         const float* mean, const float* rstd, int64_t rows, int64_t d, void* scratch,
+                         const void* dx_addend, cudaStream_t stream);
 
 // K6 embedding gather (+ optional positional table add) and scatter-add.
 int dg_embedding_fwd(int dtype, void* out, const void* table, const int64_t* idx, const void* pos_table,

@@ -95,6 +95,8 @@ typedef struct {
   int reduce_ctas;                 // unused (the reduction runs in the owner's epilogue); kept for ABI stability
   int* status;
   long long wait_cycles;
+  const void* addend;              // [M, N] bf16 (ld_addend) or null: added to this rank's partial product before the
+  int64_t ld_addend;               // scatter, so that several GEMMs can share one reduce-scatter
 } dg_gemm_rs_args;
 int dg_gemm_rs(const dg_gemm_rs_args* args, cudaStream_t stream);
 

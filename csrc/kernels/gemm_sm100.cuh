@@ -63,6 +63,10 @@ struct GemmParams {
   const int* own_flags;      // this rank's tile flags [world][tiles_per_dest]
   int64_t stage_ld;          // row stride of a staging slot (elements)
   int world;
+  // this rank's earlier partial products of the same [M, N] output (bf16, row stride addend_ld), added
+  // to every tile before it is scattered: lets several GEMMs share one reduce-scatter
+  const void* addend;
+  int64_t addend_ld;
 };
 
 template <int BN, int STAGES>
@@ -397,6 +401,13 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
 #pragma unroll
         for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
         if constexpr (SCATTER_D) {
+          if (p.addend && row_ok) {
+            const bf16* ap = reinterpret_cast<const bf16*>(p.addend) + row * p.addend_ld + col0;
+            float av[32];
+            OutVec<bf16>::load(ap, av, valid == 32 && ((reinterpret_cast<uintptr_t>(ap) & 15u) == 0), valid);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += av[e];
+          }
           if (!own_tile) return;                     // a partial for another rank: no bias, no residual
           // add the other ranks' partials in rank order (this rank's own term sits at its rank position
           // only up to fp32 rounding of the sum; partials are bf16, the accumulation is fp32)

@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(256, (KV <= 4 ? 2 : 1))
 layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __restrict__ dbeta, float* __restrict__ partial,
                            const T* __restrict__ g, const T* __restrict__ x, const T* __restrict__ gamma,
                            const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows, int d,
-                           unsigned int counter_idx) {
+                           unsigned int counter_idx, const T* __restrict__ addend) {
   constexpr int VN = Vec16<T>::N;
   extern __shared__ float s_acc[];   // [2][d]
   __shared__ int s_last;
@@ -287,6 +287,12 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
               of[e] = rs * (gf[e] * gm[e] - s1 - xh * s2);
             }
           }
+          if (addend) {   // another gradient of the same input (the residual path) joins here
+            float af[VN];
+            Vec16<T> ta; ta.load(addend + row * d + v * VN); ta.unpack(af);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) of[e] += af[e];
+          }
           Vec16<T> t2; t2.pack(of); t2.store(o + v * VN);
         }
       }
@@ -332,13 +338,14 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
 template <typename T, int KV>
 static int launch_ln_bwd_fused(void* dx, void* dgamma, void* dbeta, const void* g, const void* x, const void* gamma,
                                const float* mean, const float* rstd, int64_t rows, int64_t d, void* scratch, int grid,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const void* addend) {
   static unsigned int next_counter = 0;
   const unsigned int idx = next_counter;
   next_counter = (next_counter + 1) % kLnLaunchSlots;
   const size_t smem = (size_t)2 * d * sizeof(float);
   layernorm_bwd_fused_kernel<T, KV><<<grid, 256, smem, stream>>>((T*)dx, (T*)dgamma, (T*)dbeta, (float*)scratch, (const T*)g,
-                                                                 (const T*)x, (const T*)gamma, mean, rstd, rows, (int)d, idx);
+                                                                 (const T*)x, (const T*)gamma, mean, rstd, rows, (int)d, idx,
+                                                                 (const T*)addend);
   DG_CHECK_LAUNCH();
   return DG_OK;
 }
@@ -380,17 +387,19 @@ int launch_ln_fwd(void* y, float* mean, float* rstd, const void* x, const void* 
 template <typename T>
 int launch_ln_bwd(void* dx, void* dgamma, void* dbeta, const void* g, const void* x, const void* gamma,
                   const float* mean, const float* rstd, int64_t rows, int64_t d, void* scratch,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const void* addend = nullptr) {
   constexpr int VN = Vec16<T>::N;
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  if (dgamma && dbeta && d % VN == 0 && d / VN <= 32 * 8 && al(x) && al(g) && al(gamma) && (!dx || al(dx))) {
+  if (dgamma && dbeta && d % VN == 0 && d / VN <= 32 * 8 && al(x) && al(g) && al(gamma) && (!dx || al(dx)) &&
+      (!addend || (dx && al(addend)))) {
     const int kv = (int)((d / VN + 31) / 32);
     const int grid = ln_fused_grid(rows, kv <= 1 ? 1 : kv <= 2 ? 2 : kv <= 4 ? 4 : 8);
-    if (kv <= 1) return launch_ln_bwd_fused<T, 1>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
-    if (kv <= 2) return launch_ln_bwd_fused<T, 2>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
-    if (kv <= 4) return launch_ln_bwd_fused<T, 4>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
-    return launch_ln_bwd_fused<T, 8>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream);
+    if (kv <= 1) return launch_ln_bwd_fused<T, 1>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream, addend);
+    if (kv <= 2) return launch_ln_bwd_fused<T, 2>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream, addend);
+    if (kv <= 4) return launch_ln_bwd_fused<T, 4>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream, addend);
+    return launch_ln_bwd_fused<T, 8>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, grid, stream, addend);
   }
+  if (addend) return DG_ERR_UNSUPPORTED;   // only the fused kernel adds; the caller falls back to a separate add
   int blocks = grid_for(rows, 8);
   if (dx) {
     layernorm_bwd_dx_kernel<T><<<blocks, 256, 0, stream>>>((T*)dx, (const T*)g, (const T*)x, (const T*)gamma, mean,
@@ -437,5 +446,20 @@ extern "C" int dg_layernorm_bwd(int dtype, void* dx, void* dgamma, void* dbeta, 
   if (dtype == DG_F32) return dg::launch_ln_bwd<float>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, stream);
   if (dtype == DG_BF16)
     return dg::launch_ln_bwd<dg::bf16>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, stream);
+  return DG_ERR_BAD_ARG;
+}
+
+// Same as dg_layernorm_bwd with dx = (LayerNorm input gradient) + dx_addend: the gradient that reaches
+// the same input through the residual path joins inside the kernel. DG_ERR_UNSUPPORTED when the row
+// length or alignment needs the unfused kernels (the caller then adds separately).
+extern "C" int dg_layernorm_bwd_add(int dtype, void* dx, void* dgamma, void* dbeta, const void* g, const void* x,
+                                    const void* gamma, const float* mean, const float* rstd, int64_t rows,
+                                    int64_t d, void* scratch, const void* dx_addend, cudaStream_t stream) {
+  if (rows == 0) return DG_OK;
+  if (d <= 0 || !dx || !dgamma || !dbeta || !scratch) return DG_ERR_BAD_ARG;
+  if (dtype == DG_F32)
+    return dg::launch_ln_bwd<float>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, stream, dx_addend);
+  if (dtype == DG_BF16)
+    return dg::launch_ln_bwd<dg::bf16>(dx, dgamma, dbeta, g, x, gamma, mean, rstd, rows, d, scratch, stream, dx_addend);
   return DG_ERR_BAD_ARG;
 }

@@ -82,6 +82,7 @@ _SIGS = {
     "dg_softmax_bwd": [_i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i64, _i64, _vp],
     "dg_layernorm_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp],
     "dg_layernorm_bwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp],
+    "dg_layernorm_bwd_add": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp],
     "dg_embedding_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
     "dg_embedding_bwd": [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
     "dg_index_from_float": [_vp, _vp, _i64, _i64, _vp, _vp],
@@ -154,6 +155,9 @@ def dtype_code(dt: torch.dtype) -> int:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+ERR_UNSUPPORTED = -2      # DG_ERR_UNSUPPORTED: the kernel does not take this shape / alignment
 
 
 def check(rc: int, what: str) -> None:

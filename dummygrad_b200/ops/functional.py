@@ -1028,6 +1028,8 @@ def linear(x: Tensor, W: Tensor, b: Tensor | None = None, act: str | None = None
 
 
 class LayerNormBackward(Node):
+    fuse_input_grad = True     # dx can take the residual path's gradient of the same input inside the kernel
+
     def __init__(self, x, gamma, mean, rstd, gamma_t=None, beta_t=None):
         super().__init__()
         self.x, self.gamma, self.mean, self.rstd = x, gamma, mean, rstd
@@ -1037,8 +1039,14 @@ class LayerNormBackward(Node):
         x = self.x
         d = x.shape[-1]
         g = _grad(grads, x.shape, x.dtype, x.device)
+        addend = self._input_grad_addend
+        if addend is not None and (addend.dtype != x.dtype or addend.numel() != x.numel()):
+            addend = None
         dx, dg, db = K.layernorm_bwd(g, x, self.gamma, self.mean, self.rstd,
-                                     dgamma_out=_sink(self.gamma_t, x.dtype, d), dbeta_out=_sink(self.beta_t, x.dtype, d))
+                                     dgamma_out=_sink(self.gamma_t, x.dtype, d), dbeta_out=_sink(self.beta_t, x.dtype, d),
+                                     dx_addend=addend.reshape(x.shape) if addend is not None else None)
+        if addend is not None:
+            self._input_grad_addend = None       # consumed: dx already holds the sum
         return [dx, dg.reshape(1, d), db.reshape(1, d)]
 
     def release_variables(self):

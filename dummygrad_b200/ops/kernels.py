@@ -332,9 +332,12 @@ def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps:
     return y, mean, rstd
 
 
-def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True, dgamma_out=None, dbeta_out=None):
+def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True, dgamma_out=None, dbeta_out=None,
+                  dx_addend=None):
     """Returns (dx or None, dgamma [d] or None, dbeta [d] or None); the parameter gradients are
-    written into ``dgamma_out`` / ``dbeta_out`` (d contiguous elements of x's dtype) when given."""
+    written into ``dgamma_out`` / ``dbeta_out`` (d contiguous elements of x's dtype) when given.
+    ``dx_addend`` (same shape and dtype as x) is added to dx inside the kernel: the gradient that
+    reaches the same input through a residual connection."""
     d = x.shape[-1]
     rows = x.numel() // d
     if not _is_cuda(x):
@@ -343,6 +346,8 @@ def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True, dgam
         xh = (xf - mean[:, None]) * rstd[:, None]
         gh = gf * gamma.float().reshape(1, d)
         dx = rstd[:, None] * (gh - gh.mean(1, keepdim=True) - xh * (gh * xh).mean(1, keepdim=True))
+        if dx_addend is not None:
+            dx = dx + dx_addend.float().reshape(rows, d)
         dg = (gf * xh).sum(0)
         db = gf.sum(0)
         dg, db = dg.to(x.dtype), db.to(x.dtype)
@@ -362,9 +367,21 @@ def layernorm_bwd(g, x, gamma, mean, rstd, need_dx=True, need_dparams=True, dgam
     if need_dparams:
         scratch = torch.empty(max(int(lib.dg_layernorm_bwd_scratch_bytes(rows, d)), 4), dtype=torch.uint8,
                               device=x.device)
+    if dx_addend is not None and need_dx and need_dparams:
+        assert dx_addend.dtype == x.dtype and dx_addend.numel() == x.numel() and dx_addend.is_contiguous()
+        rc = lib.dg_layernorm_bwd_add(L.dtype_code(x.dtype), dx.data_ptr(), dgm.data_ptr(), dbt.data_ptr(), g.data_ptr(),
+                                      x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d,
+                                      scratch.data_ptr(), dx_addend.data_ptr(), L.stream_ptr())
+        if rc == 0:
+            _cnt()
+            return dx, dgm, dbt
+        if rc != L.ERR_UNSUPPORTED:
+            L.check(rc, "dg_layernorm_bwd_add")
     L.check(lib.dg_layernorm_bwd(L.dtype_code(x.dtype), L.ptr(dx), L.ptr(dgm), L.ptr(dbt), g.data_ptr(), x.data_ptr(),
                                  gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d, L.ptr(scratch),
                                  L.stream_ptr()), "dg_layernorm_bwd")
+    if dx_addend is not None and need_dx:
+        ew("ADD", dx, dx_addend.reshape(dx.shape), out=dx)
     fused = need_dparams and d % (8 if x.dtype == torch.bfloat16 else 4) == 0 and d <= (2048 if x.dtype == torch.bfloat16 else 1024)
     _cnt(1 if fused else (1 if need_dx else 0) + (2 if need_dparams else 0))
     return dx, dgm, dbt

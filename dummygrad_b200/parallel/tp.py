@@ -47,7 +47,8 @@ class GemmRsArgs(C.Structure):
                 ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64),
                 ("ldd", C.c_int64),
                 ("b_kmajor", C.c_int), ("bias_dtype", C.c_int), ("rank", C.c_int), ("world", C.c_int),
-                ("epoch", C.c_int), ("reduce_ctas", C.c_int), ("status", C.c_void_p), ("wait_cycles", C.c_longlong)]
+                ("epoch", C.c_int), ("reduce_ctas", C.c_int), ("status", C.c_void_p), ("wait_cycles", C.c_longlong),
+                ("addend", C.c_void_p), ("ld_addend", C.c_int64)]
 
 
 def _bind(lib):
@@ -163,13 +164,16 @@ def ag_gemm(ctx: TPContext, x_shard: torch.Tensor, w: torch.Tensor, bias=None, *
     return out, gb.full
 
 
-def gemm_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, *, trans_w=False, key="rs"):
-    """y_shard[M/W, N] = scatter_rows(sum over ranks of x @ W) (+ bias + residual). x [M, K_local]."""
+def gemm_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, *, trans_w=False, key="rs",
+            addend: torch.Tensor | None = None):
+    """y_shard[M/W, N] = scatter_rows(sum over ranks of (x @ W + addend)) (+ bias + residual).
+    x [M, K_local]; ``addend`` [M, N] is this rank's sum of other partial products of the same output
+    (it rides along in the epilogue, so several GEMMs share one reduce-scatter)."""
     M, Kd = x.shape
     N = w.shape[0] if trans_w else w.shape[1]
     rows = M // ctx.world
     if ctx.comm != "fused":
-        part = K.gemm2d(x, w, trans_b=trans_w)
+        part = K.gemm2d(x, w, trans_b=trans_w, residual=addend)
         if ctx.world > 1:
             out = torch.empty(rows, N, dtype=part.dtype, device=part.device)
             if part.is_cuda:
@@ -199,6 +203,9 @@ def gemm_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, bias=None, residua
     a.b_kmajor, a.bias_dtype = (1 if trans_w else 0), (L.dtype_code(bias.dtype) if bias is not None else 0)
     a.rank, a.world, a.epoch, a.reduce_ctas = ctx.rank, ctx.world, sb.epoch, ctx.comm_ctas
     a.status, a.wait_cycles = ctx.status.data_ptr(), ctx.wait_cycles
+    if addend is not None:
+        assert addend.dtype == torch.bfloat16 and addend.shape == (M, N) and addend.stride(1) == 1
+        a.addend, a.ld_addend = addend.data_ptr(), addend.stride(0)
     L.check(_bind(L.load()).dg_gemm_rs(C.byref(a), L.stream_ptr()), "dg_gemm_rs")
     K._cnt()
     return out

@@ -100,6 +100,92 @@ def gathered_linear(ctx, x: Tensor, x_full: torch.Tensor, W: Tensor, b: Tensor |
     return F._result(y, lambda: GatheredLinearBackward(ctx, x_full, K.contiguous(W.data), b is not None, key), inputs)
 
 
+class TPAttentionBlockBackward(Node):
+    """Backward of attention(gather(x) Wq + bq, gather(x) Wk + bk, gather(x) Wv + bv) on one rank's heads.
+    The three partial input gradients share ONE fused GEMM->reduce-scatter: dq Wq^T and dk Wk^T are
+    summed locally through the GEMM residual input and ride along in the epilogue of dv Wv^T."""
+
+    def __init__(self, ctx, x_full, Ws, qkv, o, lse, h_local, causal, scale, key, fused_attn):
+        super().__init__()
+        self.ctx, self.x_full, self.Ws, self.qkv, self.o, self.lse = ctx, x_full, Ws, qkv, o, lse
+        self.h_local, self.causal, self.scale, self.key, self.fused_attn = h_local, causal, scale, key, fused_attn
+
+    def apply(self, grads):
+        q, k, v = self.qkv
+        g = K.contiguous(grads[0])
+        if g.dtype != q.dtype:
+            g = K.cast(g, q.dtype)
+        g = g.reshape(q.shape)
+        if self.fused_attn:
+            dqkv = K.attention_bwd(q, k, v, self.o, g, self.lse, self.h_local, self.causal, self.scale)
+        else:
+            dqkv = _attention_bwd_chain(q, k, v, g, self.h_local, self.causal, self.scale)
+        T_ = self.x_full.shape[0]
+        outs, partial = [None], None
+        for i, (dy, W) in enumerate(zip(dqkv, self.Ws)):
+            dy2 = dy.reshape(T_, -1)
+            n = dy2.shape[1]
+            dW = K.gemm2d(self.x_full, dy2, trans_a=True)
+            db, _ = K.reduce_cols(dy2.reshape(1, T_, n), L.RED_SUM)
+            outs += [dW, db.reshape(1, n)]
+            if i < 2:
+                partial = K.gemm2d(dy2, W, trans_b=True) if partial is None else \
+                    K.gemm2d(dy2, W, trans_b=True, residual=partial, out=partial)
+            else:
+                outs[0] = tp.gemm_rs(self.ctx, dy2, W, trans_w=True, key=("bwd", self.key), addend=partial)
+        return outs
+
+    def release_variables(self):
+        self.x_full = self.qkv = self.o = self.lse = None
+
+
+def _attention_chain(q, k, v, H, causal, scale):
+    """Reference op chain on [B, S, H*dk] tensors (CPU ranks and shapes the fused kernel does not take)."""
+    B, S, D = q.shape
+    dk = D // H
+    split = lambda t: K.contiguous(t.reshape(B, S, H, dk).transpose(1, 2))  # noqa: E731
+    qd, kd, vd = split(q), split(k), split(v)
+    p = K.softmax_fwd(K.gemm2d(qd, kd, trans_b=True), None, 1 if causal else 0, scale)
+    return K.contiguous(K.gemm2d(p, vd).transpose(1, 2)).reshape(B, S, D)
+
+
+def _attention_bwd_chain(q, k, v, g, H, causal, scale):
+    B, S, D = q.shape
+    dk = D // H
+    split = lambda t: K.contiguous(t.reshape(B, S, H, dk).transpose(1, 2))  # noqa: E731
+    qd, kd, vd, gd = split(q), split(k), split(v), split(g)
+    p = K.softmax_fwd(K.gemm2d(qd, kd, trans_b=True), None, 1 if causal else 0, scale)
+    inner = F.AttentionBackward(qd, kd, vd, p, scale, causal)
+    dq, dkk, dv = inner.apply([gd])
+    back = lambda t: K.contiguous(t.transpose(1, 2)).reshape(B, S, D)  # noqa: E731
+    return back(dq), back(dkk), back(dv)
+
+
+def tp_attention_block(ctx: tp.TPContext, x: Tensor, Wq, bq, Wk, bk, Wv, bv, h_local: int, batch_seq, causal: bool,
+                       scale: float, key) -> Tensor:
+    """x [T/W, d] token shard -> this rank's heads of attention(q, k, v) as [B, S, d_local]; one
+    all-gather (inside the q GEMM) forward, one reduce-scatter (inside the last dgrad GEMM) backward."""
+    B, S = batch_seq
+    xd = K.contiguous(x.data)
+    Ws = [K.contiguous(W.data) for W in (Wq, Wk, Wv)]
+    bs = [K.contiguous(b.data).reshape(-1) for b in (bq, bk, bv)]
+    q2, x_full = tp.ag_gemm(ctx, xd, Ws[0], bs[0], key=("fwd", key))
+    k2 = K.gemm2d(x_full, Ws[1], bias=bs[1])
+    v2 = K.gemm2d(x_full, Ws[2], bias=bs[2])
+    dl = q2.shape[1]
+    q, k, v = (t.reshape(B, S, dl) for t in (q2, k2, v2))
+    fused_attn = K.attention_supported(q, h_local)
+    if fused_attn:
+        o, lse = K.attention_fwd(q, k, v, h_local, causal, scale)
+    else:
+        o, lse = _attention_chain(q, k, v, h_local, causal, scale), None
+    # the gathered activations live in a buffer that the next call with this key overwrites; the
+    # backward of this layer runs before that (layers are visited in reverse order)
+    return F._result(o, lambda: TPAttentionBlockBackward(ctx, x_full, Ws, (q, k, v), o, lse, h_local, causal, scale, key,
+                                                         fused_attn),
+                     (x, Wq, bq, Wk, bk, Wv, bv))
+
+
 class RowParallelBackward(Node):
     def __init__(self, ctx, x, w, has_bias, has_res, key):
         super().__init__()
@@ -170,11 +256,8 @@ class TPAttention(Module):
     def forward(self, x: Tensor, residual: Tensor | None = None, batch_seq=None) -> Tensor:
         B, S = batch_seq or self.batch_seq
         ctx = self.ctx
-        q, x_full = column_parallel(ctx, x, self.Wq, self.bq, key=(self.id, "q"))
-        k = gathered_linear(ctx, x, x_full, self.Wk, self.bk, key=(self.id, "k"))
-        v = gathered_linear(ctx, x, x_full, self.Wv, self.bv, key=(self.id, "v"))
-        q3, k3, v3 = (F.reshape(t, [B, S, self.dl]) for t in (q, k, v))
-        o = F.mha_core(q3, k3, v3, self.h_local, causal=self.causal, scale=1.0 / math.sqrt(self.d_k))
+        o = tp_attention_block(ctx, x, self.Wq, self.bq, self.Wk, self.bk, self.Wv, self.bv, self.h_local, (B, S),
+                               self.causal, 1.0 / math.sqrt(self.d_k), key=(self.id, "qkv"))
         return row_parallel(ctx, F.reshape(o, [B * S, self.dl]), self.Wo, self.bo, residual, key=(self.id, "o"))
 
     def parameters(self):

@@ -113,9 +113,16 @@ class Node:
     ``next_edges``.
     """
 
+    # A node whose first returned gradient (the one for next_edges[0]) can absorb another gradient of
+    # the same input sets this to True. The engine then offers the gradient that is already waiting
+    # for that input in ``self._input_grad_addend``; a node that adds it inside its own kernel sets
+    # the attribute back to None and returns the sum.
+    fuse_input_grad = False
+
     def __init__(self):
         self.next_edges: list[Edge] = []
         self._grad_owned = False
+        self._input_grad_addend = None
 
     def add_next_edge(self, function: "Node | None", slot: int = 0) -> None:
         self.next_edges.append(Edge(function, slot))
@@ -438,18 +445,31 @@ def backward(root: Tensor, retain_graph: bool = False) -> None:
         node = ready.popleft()
         slot = slots.pop(node, None)
         edges = node.next_edges
+        fused_first = False
         if slot is None:
             outs: list = [None] * len(edges)
             g = None
         else:
             g, owned = slot
             node._grad_owned = owned
+            offered = None
+            if node.fuse_input_grad and edges and edges[0].function is not None:
+                waiting = slots.get(edges[0].function)
+                if waiting is not None and waiting[0] is not ONE and waiting[0].is_contiguous():
+                    offered = node._input_grad_addend = waiting[0]
             outs = list(node.apply([g]) or [])
+            if offered is not None:
+                if node._input_grad_addend is None and outs and outs[0] is not None:
+                    fused_first = True          # outs[0] already contains the waiting gradient
+                node._input_grad_addend = None
         for i, e in enumerate(edges):
             f = e.function
             if f is None:
                 continue
             og = outs[i] if i < len(outs) else None
+            if i == 0 and fused_first and og is not None:
+                slots[f] = [og, True]
+                og = None
             if og is not None:
                 cur = slots.get(f)
                 if cur is None:

@@ -56,6 +56,16 @@ def main():
                 ref = part[rank * rows:(rank + 1) * rows] + bias.float() + res.float()
                 err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
                 assert err < 3e-2, f"gemm_rs M{M} K{Kd} N{N} trans{trans_w} rep{rep}: rel err {err}"
+                # an addend [M, N] rides along in the epilogue: scatter(sum_ranks(x W + addend))
+                add = (torch.randn(M, N, device=device) * 0.5).to(torch.bfloat16)
+                out2 = tp.gemm_rs(ctx, xk, wkl, trans_w=trans_w, key=("s", trans_w), addend=add)
+                torch.cuda.synchronize()
+                assert ctx.check_status() == 0
+                part2 = xk.float() @ wk.float().t() + add.float()
+                dist.all_reduce(part2)
+                ref2 = part2[rank * rows:(rank + 1) * rows]
+                err2 = (out2.float() - ref2).abs().max().item() / (ref2.abs().max().item() + 1e-6)
+                assert err2 < 3e-2, f"gemm_rs+addend M{M} K{Kd} N{N} trans{trans_w} rep{rep}: rel err {err2}"
     dist.barrier()
     if rank == 0:
         print(f"TP_WORKER_OK world={world}")
