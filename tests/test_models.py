@@ -177,3 +177,36 @@ def test_bf16_model_step(device):
         opt.step()
         losses.append(loss.item())
     assert all(math.isfinite(v) for v in losses) and losses[-1] < losses[0], losses
+
+
+def test_residual_gradient_joins_inside_layernorm_backward(device):
+    """x feeds a LayerNorm branch and a residual connection: the engine hands the residual path's
+    gradient to LayerNormBackward, which returns the sum (no separate add); values match autograd."""
+    import torch.nn.functional as TF
+    from dummygrad_b200.ops import functional as F
+    torch.manual_seed(0)
+    xv, wv = torch.randn(6, 16), torch.randn(16, 16) * 0.3
+    gam, bet = 1 + 0.1 * torch.randn(1, 16), 0.1 * torch.randn(1, 16)
+    x, W = T(xv, device), T(wv, device)
+    g_, b_ = T(gam, device), T(bet, device)
+    calls = []
+    orig = F.LayerNormBackward.apply
+
+    def spy(self, grads):
+        calls.append(self._input_grad_addend is not None)
+        return orig(self, grads)
+
+    F.LayerNormBackward.apply = spy
+    try:
+        y = F.linear(F.layer_norm(x, g_, b_), W, None, residual=x)
+        dg.simple_sum(dg.mul(y, y)).backward()
+    finally:
+        F.LayerNormBackward.apply = orig
+    assert calls == [True], "the waiting residual gradient must be offered to the LayerNorm backward node"
+    xt, wt = xv.clone().requires_grad_(True), wv.clone().requires_grad_(True)
+    gt, bt = gam.clone().requires_grad_(True), bet.clone().requires_grad_(True)
+    yt = TF.layer_norm(xt, (16,), gt.reshape(-1), bt.reshape(-1), 1e-5) @ wt + xt
+    (yt * yt).sum().backward()
+    close(x.grad.data, xt.grad, 1e-4, "dx")
+    close(W.grad.data, wt.grad, 1e-4, "dW")
+    close(g_.grad.data, gt.grad, 1e-4, "dgamma")
