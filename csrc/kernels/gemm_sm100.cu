@@ -82,9 +82,6 @@ void fill_params(GemmParams* p, const dg_gemm_args* a) {
   p->a_bcast = (a->a_bs == 0);
   p->b_bcast = (a->b_bs == 0);
   p->bias_bs = a->bias_bs;
-  static int dbg = -1;
-  if (dbg < 0) { const char* e = getenv("DG_GEMM_DEBUG"); dbg = e ? atoi(e) : 0; }
-  p->debug = dbg;
 }
 
 // Output (and saved pre-activation) maps for the staged TMA-store epilogue; sets p->tma_store / tma_aux.
@@ -197,7 +194,13 @@ extern "C" int dg_gemm_sm100(const dg_gemm_args* a, cudaStream_t stream) {
   fill_params(&p, a);
   CUtensorMap tmD, tmAux;
   build_output_maps(&tmD, &tmAux, &p, a);
-  if (p.debug & 16) p.tma_store = p.tma_aux = 0;   // timing experiments: direct global stores
+  {
+    // DG_GEMM_DIRECT_STORE=1: epilogue stores straight from registers instead of through shared memory
+    // and TMA (the path taken anyway when the output does not meet the TMA alignment rules)
+    static int direct = -1;
+    if (direct < 0) { const char* e = getenv("DG_GEMM_DIRECT_STORE"); direct = (e && e[0] == '1') ? 1 : 0; }
+    if (direct) p.tma_store = p.tma_aux = 0;
+  }
   if (BN == 256) return dispatch_layout<256, 4>(a, tmA, tmB, tmD, tmAux, p, stream);
   return dispatch_layout<128, 6>(a, tmA, tmB, tmD, tmAux, p, stream);
 }
