@@ -515,8 +515,12 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
 #pragma unroll 1
           for (int pass = 0; pass < npass; ++pass) {
             const bool aux_pass = two_pass && pass == 0;
-            if (lane == 0) bulk_wait_read0();            // previous store has finished reading the slab
-            __syncwarp();
+            // The slab row of this thread is built in registers first; only then does the warp wait
+            // for the previous TMA store to finish reading the slab, so that its latency overlaps the
+            // TMEM loads and the epilogue math of this slab.
+            uint4 pk[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) pk[q] = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int k = 0; k < kCh; ++k) {
               const int ch = s0 + k;
@@ -532,19 +536,21 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
               if (sizeof(OutT) == 2 || aux_pass) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  uint4 pk;
-                  __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+                  __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk[k * 4 + q]);
 #pragma unroll
                   for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1]);
-                  *reinterpret_cast<uint4*>(slab_row + (((k * 4 + q) ^ sw) << 4)) = pk;
                 }
               } else {
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
-                  *reinterpret_cast<float4*>(slab_row + ((q ^ sw) << 4)) =
-                      make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                  pk[q] = make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
+                                     __float_as_uint(v[q * 4 + 3]));
               }
             }
+            if (lane == 0) bulk_wait_read0();            // previous store has finished reading the slab
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(slab_row + ((q ^ sw) << 4)) = pk[q];
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && col_slab < p.N) {
