@@ -325,9 +325,10 @@ def run_reference(args) -> dict:
     reference is a single-threaded CPU library, so only the two small configurations can run."""
     ref_src = os.path.join(ROOT, "baseline", "_ref", "src")
     if not os.path.isdir(ref_src):
-        if os.path.isdir("/root/reference/src"):
+        upstream = os.environ.get("DG_REFERENCE_SRC", "")       # a checkout of the reference's src/ directory
+        if upstream and os.path.isdir(upstream):
             import shutil
-            shutil.copytree("/root/reference/src", ref_src)
+            shutil.copytree(upstream, ref_src)
         else:
             return {"impl": "reference", "unavailable": "reference headers not present under baseline/_ref/src"}
     if args.config in ("gpt350m", "gpt1p3b"):

@@ -10,13 +10,13 @@ import pytest
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_DIRS = [os.path.join(ROOT, "baseline", "_ref", "src"), "/root/reference/src"]
+REF_DIRS = [os.path.join(ROOT, "baseline", "_ref", "src"), os.environ.get("DG_REFERENCE_SRC", "")]
 LIB = os.path.join(ROOT, "dummygrad_b200", "lib")
 
 
 def _ref_src():
     for d in REF_DIRS:
-        if os.path.isfile(os.path.join(d, "test_all.cpp")):
+        if d and os.path.isfile(os.path.join(d, "test_all.cpp")):
             return d
     return None
 
