@@ -238,13 +238,17 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
   for (int64_t row = warp; row < rows; row += nwarps) {
     const T* xr = x + row * d;
     const T* gr = g + row * d;
-    Vec16<T> xv[KV], gv[KV];
+    Vec16<T> xv[KV], gv[KV], av[KV];    // av: the residual path's gradient, requested together with x and g
 #pragma unroll
     for (int k = 0; k < KV; ++k) {
       const int v = lane + 32 * k;
-      if (v < nvec) { xv[k].load(xr + v * VN); gv[k].load(gr + v * VN); }
+      if (v < nvec) {
+        xv[k].load(xr + v * VN); gv[k].load(gr + v * VN);
+        if (addend) av[k].load(addend + row * d + v * VN);
+      }
     }
     const float mu = mean[row], rs = rstd[row];
+    const float nmr = -mu * rs;      // xhat = x * rs + nmr
     // pass 1 over registers: xhat and g*gamma overwrite the cached x and g (packed back to the input
     // type), so the second pass needs neither gamma nor the statistics again
     float s1 = 0.f, s2 = 0.f;
@@ -257,7 +261,7 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
         Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
-          const float xh = (xf[e] - mu) * rs, gh = gf[e] * gm[e];
+          const float xh = fmaf(xf[e], rs, nmr), gh = gf[e] * gm[e];
           s1 += gh; s2 = fmaf(gh, xh, s2);
           adg[k][e] = fmaf(gf[e], xh, adg[k][e]); adb[k][e] += gf[e];
           xf[e] = xh; gf[e] = gh;
@@ -267,6 +271,7 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
     }
     s1 = warp_sum(s1) / (float)d;
     s2 = warp_sum(s2) / (float)d;
+    const float cA = -rs * rs * s2, cB = -rs * (s1 + s2 * nmr);
     if (dx) {
       T* o = dx + row * d;
 #pragma unroll
@@ -282,14 +287,13 @@ layernorm_bwd_fused_kernel(T* __restrict__ dx, T* __restrict__ dgamma, T* __rest
             float gm[VN];
             Vec16<T> t; t.load(gamma + v * VN); t.unpack(gm);
 #pragma unroll
-            for (int e = 0; e < VN; ++e) {
-              const float xh = (xf[e] - mu) * rs;
-              of[e] = rs * (gf[e] * gm[e] - s1 - xh * s2);
-            }
+            // dx = rs * (g*gamma - s1 - xhat*s2) with xhat = x*rs + nmr, regrouped to three operations:
+            //      = g * (gamma*rs) + x * cA + cB
+            for (int e = 0; e < VN; ++e) of[e] = fmaf(gf[e], gm[e] * rs, fmaf(xf[e], cA, cB));
           }
           if (addend) {   // another gradient of the same input (the residual path) joins here
             float af[VN];
-            Vec16<T> ta; ta.load(addend + row * d + v * VN); ta.unpack(af);
+            av[k].unpack(af);
 #pragma unroll
             for (int e = 0; e < VN; ++e) of[e] += af[e];
           }
