@@ -12,7 +12,7 @@ namespace dg {
 
 constexpr int kLnMaxVec = 8;  // vectors cached per lane
 
-template <typename T, bool CACHED>
+template <typename T, bool CACHED, int KV = kLnMaxVec>
 __global__ void __launch_bounds__(256) layernorm_fwd_kernel(T* __restrict__ y, float* __restrict__ mean,
                                                             float* __restrict__ rstd, const T* __restrict__ x,
                                                             const T* __restrict__ gamma, const T* __restrict__ beta,
@@ -27,10 +27,10 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(T* __restrict__ y, f
     T* yr = y + row * d;
     float mu, rs;
     if constexpr (CACHED) {
-      float vals[kLnMaxVec][VN];
+      float vals[KV][VN];
       float s = 0.f;
 #pragma unroll
-      for (int k = 0; k < kLnMaxVec; ++k) {
+      for (int k = 0; k < KV; ++k) {
         int64_t v = lane + 32 * k;
         if (v < nvec) {
           Vec16<T> t; t.load(xr + v * VN); t.unpack(vals[k]);
@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(T* __restrict__ y, f
       mu = warp_sum(s) / (float)d;
       float q = 0.f;
 #pragma unroll
-      for (int k = 0; k < kLnMaxVec; ++k) {
+      for (int k = 0; k < KV; ++k) {
         int64_t v = lane + 32 * k;
         if (v < nvec) {
 #pragma unroll
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(T* __restrict__ y, f
       }
       rs = rsqrtf(warp_sum(q) / (float)d + eps);
 #pragma unroll
-      for (int k = 0; k < kLnMaxVec; ++k) {
+      for (int k = 0; k < KV; ++k) {
         int64_t v = lane + 32 * k;
         if (v < nvec) {
           float gf[VN], bf[VN], of[VN];
@@ -378,9 +378,17 @@ int launch_ln_fwd(void* y, float* mean, float* rstd, const void* x, const void* 
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   bool cached = (d % VN == 0) && (d / VN <= 32 * kLnMaxVec) && al(x) && al(y) && al(gamma) && al(beta);
   int blocks = grid_for(rows, 8);
-  if (cached)
-    layernorm_fwd_kernel<T, true><<<blocks, 256, 0, stream>>>((T*)y, mean, rstd, (const T*)x, (const T*)gamma,
-                                                              (const T*)beta, rows, d, eps);
+  if (cached) {
+    // registers for exactly as many 16-byte vectors per lane as the row needs (more resident warps)
+    const int kv = (int)((d / VN + 31) / 32);
+#define DG_LN_FWD(KVV) layernorm_fwd_kernel<T, true, KVV><<<blocks, 256, 0, stream>>>((T*)y, mean, rstd, (const T*)x, \
+                                                        (const T*)gamma, (const T*)beta, rows, d, eps)
+    if (kv <= 1) DG_LN_FWD(1);
+    else if (kv <= 2) DG_LN_FWD(2);
+    else if (kv <= 4) DG_LN_FWD(4);
+    else DG_LN_FWD(8);
+#undef DG_LN_FWD
+  }
   else
     layernorm_fwd_kernel<T, false><<<blocks, 256, 0, stream>>>((T*)y, mean, rstd, (const T*)x, (const T*)gamma,
                                                                (const T*)beta, rows, d, eps);
