@@ -1,0 +1,65 @@
+"""The fused reduce-scatter / update / push protocol on CPU processes over shared memory: epoch-
+valued flags, deterministic result, and bounded waits that turn a skipped signal into a status
+code instead of a hang (nothing here touches a GPU)."""
+import os
+import time
+
+import numpy as np
+import torch.multiprocessing as mp
+
+from dummygrad_b200.parallel import hostsim as H
+
+W, N, LR = 3, 3 * 64, 0.1
+
+
+def _rank(rank, name, epochs, skip_at, q):
+    mem = H.HostPeerMemory(name, W, N, create=False)
+    codes = []
+    for ep in range(1, epochs + 1):
+        rng = np.random.default_rng(100 * ep + rank)
+        mem.grads[rank, :] = rng.standard_normal(N).astype(np.float32)
+        skip = (skip_at is not None and ep == skip_at[0] and rank == skip_at[1])
+        code = H.fused_step(mem, rank, ep, LR, timeout_s=1.0, skip_ready_signal=skip)
+        codes.append(code)
+        if code != H.OK:
+            break
+    q.put((rank, codes, mem.params[rank].copy().tolist()))
+    mem.close()
+
+
+def _run(epochs, skip_at=None):
+    name = f"dg_hostsim_{os.getpid()}_{int(time.time() * 1e3) % 100000}"
+    owner = H.HostPeerMemory(name, W, N, create=True)
+    try:
+        ctx = mp.get_context("spawn")
+        q = ctx.SimpleQueue()
+        procs = [ctx.Process(target=_rank, args=(r, name, epochs, skip_at, q)) for r in range(W)]
+        [p.start() for p in procs]
+        out = sorted(q.get() for _ in range(W))
+        [p.join(30) for p in procs]
+        return out
+    finally:
+        owner.close(unlink=True)
+
+
+def test_protocol_matches_plain_sgd_and_is_identical_on_every_rank():
+    out = _run(4)
+    ref = np.zeros(N, dtype=np.float32)
+    for ep in range(1, 5):
+        g = sum(np.random.default_rng(100 * ep + r).standard_normal(N).astype(np.float32) for r in range(W))
+        ref -= LR * (g / W)
+    for rank, codes, params in out:
+        assert codes == [H.OK] * 4
+        np.testing.assert_allclose(np.array(params, dtype=np.float32), ref, rtol=0, atol=1e-5)
+    assert out[0][2] == out[1][2] == out[2][2]
+
+
+def test_skipped_signal_becomes_a_status_code_not_a_hang():
+    t0 = time.time()
+    out = _run(3, skip_at=(2, 1))          # rank 1 never publishes "ready" in epoch 2
+    assert time.time() - t0 < 20
+    codes = {rank: c for rank, c, _ in out}
+    assert codes[0][:1] == [H.OK] and codes[2][:1] == [H.OK]
+    # every rank, rank 1 included (its own pad never got the flag either), gives up on rank 1 in epoch 2
+    for r in range(W):
+        assert codes[r][1] == (H.ERR_READY_TIMEOUT | 1), codes
